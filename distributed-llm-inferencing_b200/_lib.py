@@ -75,8 +75,8 @@ SIGNATURES = {
     "dli_concat_cast": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "dli_rows_bias_f32": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "dli_latent_prep": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _f, _vp, _vp,
-                             _i, _i, _vp]),
-    "dli_latent_q_absorb": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+                             _i, _i, _i, _vp]),
+    "dli_latent_q_absorb": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "dli_latent_v_up": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "dli_latent_expand": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "dli_sigmoid_gate": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _vp]),
@@ -97,11 +97,16 @@ SIGNATURES = {
     "dli_silu_mul": (_i, [_vp, _vp, _i, _i, _i, _i, _vp]),
     "dli_attn_prep_append": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i,
                                   _vp, _vp, _f, _vp, _vp, _vp, _vp, _i, _i, _vp]),
-    "dli_attn_ragged": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _i,
+    "dli_attn_ragged": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp, _i,
                              _i, _vp, _vp, _i, _i, _vp, _i, _vp]),
     "dli_attn_ragged_tc_supported": (_i, [_i, _i, _i]),
-    "dli_attn_ragged_tc": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _vp, _i,
+    "dli_attn_ragged_tc": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp, _i,
                                 _i, _vp, _vp, _vp]),
+    "dli_postnorm_vec_add": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp]),
+    "dli_token_side_act": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+    "dli_token_side": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp]),
+    "dli_delta_rule_ragged": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _f, _f, _i, _vp]),
+    "dli_head_rmsnorm_gate": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _i, _i, _i, _i, _vp]),
     "dli_mlstm_parallel_scratch_floats": (_sz, [_i, _i, _i, _i]),
     "dli_mlstm_ragged_parallel": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i,
                                        _vp, _vp, _f, _vp, _f, _vp, _vp, _vp, _i, _vp]),

@@ -35,6 +35,7 @@ SOURCES = [
     "latent_attn.cu",
     "mamba2.cu",
     "moe.cu",
+    "delta_rule.cu",
 ]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]

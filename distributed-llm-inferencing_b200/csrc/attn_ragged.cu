@@ -7,7 +7,7 @@
 //     head's output at position i is turned back by -i,
 //   - key/value heads shared by groups of query heads, key size D and value size V independent,
 //   - a chunk mask (position i sees j <= i in its own chunk of `chunk` positions, counted from position 0) and/or
-//     a sliding window (j > i - window),
+//     a sliding window (j > i - window) that may also keep the sequence's first tokens (j < first) in view,
 //   - a sink: one more term exp(sink[h]) in the softmax denominator, without key or value,
 //   - an output gate: head h's output times sigmoid(gate[row, h]).
 // Scores, softmax weights and the accumulation are fp32; the cache holds E (bf16 or float).
@@ -109,6 +109,7 @@ struct AttnRun {
   int H, G, D, V;
   float scale;
   int chunk, window;        // 0 = off
+  int first;                // with a chunk or window: positions below `first` stay visible whatever the lower bound says
   const float* sink;        // [H] or NULL
   int ldp, g_off;           // gate column of the packed projection row, g_off < 0: no gate
   const float* cos_v;       // [positions, V/2] or NULL: turn the output back
@@ -190,12 +191,16 @@ attn_ragged_kernel(const float* __restrict__ qbuf, const E* __restrict__ kc, con
   if (a.chunk > 0) lo = (pos / a.chunk) * a.chunk;
   if (a.window > 0 && pos - a.window + 1 > lo) lo = pos - a.window + 1;
   for (int c = tid; c < a.D; c += kAttnThreads) q[c] = qbuf[((size_t)row * a.H + h) * a.D + c] * a.scale;
-  int jb = lo, je = pos;    // this CTA's keys
+  // the visible keys are positions [0, nf) and [lo, pos]; the loops below walk them as one range of indices
+  // [lo - nf, pos], an index below lo standing for position index - (lo - nf)
+  const int nf = min(a.first, lo), shift = lo - nf;
+  int jb = shift, je = pos;    // this CTA's keys
   if (a.splits > 1) {
-    const int per = (pos - lo + a.splits) / a.splits;
-    jb = lo + (int)blockIdx.z * per;
+    const int per = (pos - shift + a.splits) / a.splits;
+    jb = shift + (int)blockIdx.z * per;
     je = min(pos, jb + per - 1);
   }
+  auto key_pos = [&](int idx) { return idx < lo ? idx - shift : idx; };
 
   const bool vec = attn_vec_values(a.V, a.ldv);
   const int groups = attn_value_groups(a.V, a.ldv);
@@ -219,7 +224,8 @@ attn_ragged_kernel(const float* __restrict__ qbuf, const E* __restrict__ kc, con
     {
       float dpart = 0.f;
       if (j <= je) {
-        const E* kr = kc + (((size_t)pt[j / a.page_size] * a.G + g) * a.page_size + j % a.page_size) * a.D;
+        const int jp = key_pos(j);
+        const E* kr = kc + (((size_t)pt[jp / a.page_size] * a.G + g) * a.page_size + jp % a.page_size) * a.D;
         const int len = a.D / tpk;
         dpart = dot_row(q + part * len, kr + part * len, len);
       }
@@ -253,7 +259,7 @@ attn_ragged_kernel(const float* __restrict__ qbuf, const E* __restrict__ kc, con
         float wj[KR];
 #pragma unroll
         for (int u = 0; u < KR; ++u) {
-          const int ju = jj + u * groups, jk = j0 + min(ju, cnt - 1);
+          const int ju = jj + u * groups, jk = key_pos(j0 + min(ju, cnt - 1));
           vr[u] = vc + (((size_t)pt[jk / a.page_size] * a.G + g) * a.page_size + jk % a.page_size) * a.ldv;
           wj[u] = ju < cnt ? p[ju] : 0.f;
         }
@@ -447,6 +453,10 @@ attn_ragged_tc_kernel(const float* __restrict__ qbuf, const bf16* __restrict__ k
     return lo;
   };
   const int t_begin = row_lo(p0) / kRtTile, t_end = p_last / kRtTile + 1;
+  // tiles of the kept first positions that lie below the first tile of the mask's range come before it
+  const int t_first = min(t_begin, (min(a.first, row_lo(p0)) + kRtTile - 1) / kRtTile);
+  const int n_iter = t_first + (t_end - t_begin);
+  auto tile_of = [&](int it) { return it < t_first ? it : t_begin + (it - t_first); };
   const int gq = lane >> 2, t4 = lane & 3;
   const int qabs[2] = {p0 + warp * 16 + gq, p0 + warp * 16 + gq + 8};
   const int qlo[2] = {row_lo(qabs[0]), row_lo(qabs[1])};
@@ -460,19 +470,19 @@ attn_ragged_tc_kernel(const float* __restrict__ qbuf, const bf16* __restrict__ k
   for (int i = 0; i < DV / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
   uint32_t qf[DK / 16][4];
 
-  load_tile(t_begin, 0);
+  load_tile(tile_of(0), 0);
   cp_async_commit();
-  for (int tile = t_begin; tile < t_end; ++tile) {
-    const int stage = (tile - t_begin) & 1;
-    if (tile + 1 < t_end) {
-      load_tile(tile + 1, stage ^ 1);
+  for (int it = 0; it < n_iter; ++it) {
+    const int tile = tile_of(it), stage = it & 1;
+    if (it + 1 < n_iter) {
+      load_tile(tile_of(it + 1), stage ^ 1);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
       cp_async_wait<0>();
     }
     __syncthreads();
-    if (tile == t_begin) {
+    if (it == 0) {
 #pragma unroll
       for (int kk = 0; kk < DK / 16; ++kk) {
         const int mi = lane >> 3;
@@ -502,7 +512,7 @@ attn_ragged_tc_kernel(const float* __restrict__ qbuf, const bf16* __restrict__ k
         for (int x = 0; x < 4; ++x) {
           const int tok = tk0 + j * 8 + 2 * t4 + (x & 1);
           const int r = x >> 1;
-          if (tok > qabs[r] || tok < qlo[r]) s[j][x] = -INFINITY;
+          if (tok > qabs[r] || (tok < qlo[r] && tok >= a.first)) s[j][x] = -INFINITY;
         }
     }
     uint32_t pa[4][4];
@@ -612,8 +622,8 @@ int dli_attn_prep_append(const void* proj, float* qbuf, void* k_cache, void* v_c
 
 int dli_attn_ragged(const float* qbuf, const void* k_cache, const void* v_cache, const void* proj, void* out,
                     const int32_t* row_ent, const int32_t* ent, const int32_t* page_table, int max_pages, int page_size,
-                    int rows, int H, int G, int D, int V, float scale, int chunk, int window, const float* sink, int ldp,
-                    int g_off, const float* cos_v, const float* sin_v, int ldv, int splits, float* part, int dt,
+                    int rows, int H, int G, int D, int V, float scale, int chunk, int window, int first, const float* sink,
+                    int ldp, int g_off, const float* cos_v, const float* sin_v, int ldv, int splits, float* part, int dt,
                     dli_stream_t stream) {
   DLI_CHECK_ARG(qbuf && k_cache && v_cache && out && row_ent && ent && page_table, "dli_attn_ragged: null pointer");
   DLI_CHECK_ARG(splits >= 1 && splits <= 64 && (splits == 1 || part), "dli_attn_ragged: %d key splits (1..64, with scratch)", splits);
@@ -624,8 +634,9 @@ int dli_attn_ragged(const float* qbuf, const void* k_cache, const void* v_cache,
                 kAttnThreads * kAttnMaxVPerThread);
   DLI_CHECK_ARG(dt == 0 || dt == 1, "element type %d: 0 = bf16, 1 = float", dt);
   if (rows <= 0) return DLI_OK;
-  AttnRun a{row_ent, ent, page_table, max_pages, page_size, H, G, D, V, scale, chunk, window, sink, ldp, g_off, cos_v, sin_v,
-            ldv ? ldv : V, splits, part};
+  DLI_CHECK_ARG(first >= 0, "dli_attn_ragged: %d kept first positions", first);
+  AttnRun a{row_ent, ent, page_table, max_pages, page_size, H, G, D, V, scale, chunk, window, first, sink, ldp, g_off, cos_v,
+            sin_v, ldv ? ldv : V, splits, part};
   const int groups = attn_value_groups(V, ldv ? ldv : V);
   const size_t smem = sizeof(float) * (D + kAttnThreads + 8 + (size_t)groups * V);
   DLI_CHECK_ARG(smem <= 48 * 1024, "dli_attn_ragged: key size %d needs %zu bytes of shared memory", D, smem);
@@ -646,15 +657,16 @@ int dli_attn_ragged_tc_supported(int D, int V, int dt) {
 
 int dli_attn_ragged_tc(const float* qbuf, const void* k_cache, const void* v_cache, const void* proj, void* out,
                        const int32_t* ent, const int32_t* tiles, int n_tiles, const int32_t* page_table, int max_pages,
-                       int page_size, int H, int G, int D, int V, float scale, int chunk, int window, const float* sink,
-                       int ldp, int g_off, const float* cos_v, const float* sin_v, dli_stream_t stream) {
+                       int page_size, int H, int G, int D, int V, float scale, int chunk, int window, int first,
+                       const float* sink, int ldp, int g_off, const float* cos_v, const float* sin_v, dli_stream_t stream) {
   DLI_CHECK_ARG(qbuf && k_cache && v_cache && out && ent && tiles && page_table, "dli_attn_ragged_tc: null pointer");
   DLI_CHECK_ARG(g_off < 0 || proj, "dli_attn_ragged_tc: a gate needs the projection rows");
   DLI_CHECK_ARG(H > 0 && G > 0 && H % G == 0 && scale > 0.f, "dli_attn_ragged_tc: H=%d G=%d scale=%g", H, G, scale);
   if (!dli_attn_ragged_tc_supported(D, V, 0))
     return dli::fail(DLI_ERR_UNSUPPORTED, "dli_attn_ragged_tc: key size %d with value size %d has no tensor-core tile", D, V);
   if (n_tiles <= 0) return DLI_OK;
-  AttnRun a{nullptr, ent, page_table, max_pages, page_size, H, G, D, V, scale, chunk, window, sink, ldp, g_off, cos_v, sin_v, V, 1, nullptr};
+  DLI_CHECK_ARG(first >= 0, "dli_attn_ragged_tc: %d kept first positions", first);
+  AttnRun a{nullptr, ent, page_table, max_pages, page_size, H, G, D, V, scale, chunk, window, first, sink, ldp, g_off, cos_v, sin_v, V, 1, nullptr};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (D == 64 && V == 64) return launch_ragged_tc<64, 64>(qbuf, k_cache, v_cache, proj, out, tiles, n_tiles, a, s);
   if (D == 128 && V == 128) return launch_ragged_tc<128, 128>(qbuf, k_cache, v_cache, proj, out, tiles, n_tiles, a, s);

@@ -10,8 +10,10 @@
 //   dli_latent_prep      c_q = rmsnorm(W_dq h) -> operand of the query up-projection; c, rotated k_r -> the pool
 //   dli_latent_q_absorb  q~[h] = [U_k[h]^T q_n[h] | rot(q_r[h])] -> fp32 query rows of size K + R
 //   dli_latent_v_up      out[h] = (U_v[h] o~[h]) * sigmoid(gate[h])   with o~ the attention output in the latent
-// Rotation: interleaved pairs (2i, 2i+1) from a host-made fp32 cos/sin table [positions, R/2].  Norms, rotation and
-// the absorbed queries are fp32; E (bf16 or float) is the element type of projections and the pool.
+// Rotation: from a host-made fp32 cos/sin table [positions, R/2]; pair i is entries (2i, 2i+1) (`halves` == 0,
+// interleaved) or entries (i, i + R/2) (`halves` != 0).  A model without a query latent (Q == 0) projects its
+// queries directly and skips that part of dli_latent_prep.  Norms, rotation and the absorbed queries are fp32; E
+// (bf16 or float) is the element type of projections and the pool.
 #include <math.h>
 
 #include "common.cuh"
@@ -48,6 +50,7 @@ struct LatentPrep {
   float eps;
   const float* cos_t;       // [positions, R/2]
   const float* sin_t;
+  int halves;               // pair i of the rotated part: 0 = entries (2i, 2i+1), 1 = entries (i, i + R/2)
 };
 
 // One CTA per row.
@@ -63,33 +66,37 @@ latent_prep_kernel(const E* __restrict__ proj, E* __restrict__ cq, E* __restrict
   const size_t page = a.page_table[(size_t)e.x * a.max_pages + pos / a.page_size];
   E* dst = pool + (page * a.page_size + pos % a.page_size) * (size_t)(a.K + a.R);
   const E* pr = proj + (size_t)row * a.ldp;
-  float ss = 0.f;
-  for (int c = tid; c < a.Q; c += blockDim.x) { const float v = l_to_f(pr[a.q_off + c]); ss += v * v; }
-  ss = l_block_sum(ss, red);
-  float r = 1.f / sqrtf(ss / a.Q + a.eps);
-  for (int c = tid; c < a.Q; c += blockDim.x) cq[(size_t)row * a.Q + c] = l_from_f<E>(l_to_f(pr[a.q_off + c]) * r * a.qn[c]);
+  float ss = 0.f, r;
+  if (a.Q > 0) {
+    for (int c = tid; c < a.Q; c += blockDim.x) { const float v = l_to_f(pr[a.q_off + c]); ss += v * v; }
+    ss = l_block_sum(ss, red);
+    r = 1.f / sqrtf(ss / a.Q + a.eps);
+    for (int c = tid; c < a.Q; c += blockDim.x) cq[(size_t)row * a.Q + c] = l_from_f<E>(l_to_f(pr[a.q_off + c]) * r * a.qn[c]);
+  }
   ss = 0.f;
   for (int c = tid; c < a.K; c += blockDim.x) { const float v = l_to_f(pr[a.kv_off + c]); ss += v * v; }
   ss = l_block_sum(ss, red);
   r = 1.f / sqrtf(ss / a.K + a.eps);
   for (int c = tid; c < a.K; c += blockDim.x) dst[c] = l_from_f<E>(l_to_f(pr[a.kv_off + c]) * r * a.kn[c]);
   for (int i = tid; i < a.R / 2; i += blockDim.x) {
-    const float u = l_to_f(pr[a.kv_off + a.K + 2 * i]), v = l_to_f(pr[a.kv_off + a.K + 2 * i + 1]);
+    const int iu = a.halves ? i : 2 * i, iv = a.halves ? i + a.R / 2 : 2 * i + 1;
+    const float u = l_to_f(pr[a.kv_off + a.K + iu]), v = l_to_f(pr[a.kv_off + a.K + iv]);
     const float c = a.cos_t[(size_t)pos * (a.R / 2) + i], s = a.sin_t[(size_t)pos * (a.R / 2) + i];
-    dst[a.K + 2 * i] = l_from_f<E>(u * c - v * s);
-    dst[a.K + 2 * i + 1] = l_from_f<E>(v * c + u * s);
+    dst[a.K + iu] = l_from_f<E>(u * c - v * s);
+    dst[a.K + iv] = l_from_f<E>(v * c + u * s);
   }
 }
 
 constexpr int kLatRows = 8;  // rows of a step that share one pass over a head's up-projection
 
-// qbuf[row, h, 0:K] = sum_d q[row, h, d] * uk[h, d, :],  qbuf[row, h, K:K+R] = rot(q[row, h, D:D+R], pos).
+// qbuf[row, h, 0:K] = sum_d q[row, h, d] * uk[h, d, :],  qbuf[row, h, K:K+R] = rot(q[row, h, D:D+R], pos); the rows of
+// q are ldq elements apart (queries that are columns of a wider projection).
 // Grid (row tiles, heads); threads across the K outputs, the head's D query entries of the tile's rows in shared memory.
 template <typename E>
 __global__ void __launch_bounds__(256)
 latent_q_absorb_kernel(const E* __restrict__ q, const E* __restrict__ uk, float* __restrict__ qbuf,
                        const int32_t* __restrict__ row_ent, const int32_t* __restrict__ ent, const float* __restrict__ cos_t,
-                       const float* __restrict__ sin_t, int rows, int H, int D, int R, int K) {
+                       const float* __restrict__ sin_t, int rows, int H, int D, int R, int K, int halves, int ldq) {
   extern __shared__ float qs[];  // [kLatRows][D]
   pdl_wait();
   pdl_trigger();
@@ -97,7 +104,7 @@ latent_q_absorb_kernel(const E* __restrict__ q, const E* __restrict__ uk, float*
   const int nr = min(kLatRows, rows - r0);
   for (int i = tid; i < kLatRows * D; i += blockDim.x) {
     const int r = i / D, d = i - r * D;
-    qs[i] = r < nr ? l_to_f(q[((size_t)(r0 + r) * H + h) * (D + R) + d]) : 0.f;
+    qs[i] = r < nr ? l_to_f(q[(size_t)(r0 + r) * ldq + h * (D + R) + d]) : 0.f;
   }
   __syncthreads();
   const E* w = uk + (size_t)h * D * K;
@@ -124,12 +131,13 @@ latent_q_absorb_kernel(const E* __restrict__ q, const E* __restrict__ uk, float*
     const int row = r0 + r;
     const int4 e = reinterpret_cast<const int4*>(ent)[row_ent[row]];
     const int pos = e.w + (row - e.y);
-    const E* src = q + ((size_t)row * H + h) * (D + R) + D;
-    const float u = l_to_f(src[2 * p]), v = l_to_f(src[2 * p + 1]);
+    const E* src = q + (size_t)row * ldq + h * (D + R) + D;
+    const int iu = halves ? p : 2 * p, iv = halves ? p + R / 2 : 2 * p + 1;
+    const float u = l_to_f(src[iu]), v = l_to_f(src[iv]);
     const float c = cos_t[(size_t)pos * (R / 2) + p], s = sin_t[(size_t)pos * (R / 2) + p];
     float* dst = qbuf + ((size_t)row * H + h) * (K + R) + K;
-    dst[2 * p] = u * c - v * s;
-    dst[2 * p + 1] = v * c + u * s;
+    dst[iu] = u * c - v * s;
+    dst[iv] = v * c + u * s;
   }
 }
 
@@ -218,14 +226,14 @@ extern "C" {
 int dli_latent_prep(const void* proj, void* cq, void* pool, const int32_t* row_ent, const int32_t* ent,
                     const int32_t* page_table, int max_pages, int page_size, int rows, int Q, int K, int R, int ldp,
                     int q_off, int kv_off, const float* q_norm, const float* kv_norm, float eps, const float* cos_t,
-                    const float* sin_t, int table_len, int dt, dli_stream_t stream) {
-  DLI_CHECK_ARG(proj && cq && pool && row_ent && ent && page_table && q_norm && kv_norm, "dli_latent_prep: null pointer");
-  DLI_CHECK_ARG(Q > 0 && K > 0 && R >= 0 && R % 2 == 0 && (R == 0 || (cos_t && sin_t && table_len > 0)),
+                    const float* sin_t, int table_len, int halves, int dt, dli_stream_t stream) {
+  DLI_CHECK_ARG(proj && pool && row_ent && ent && page_table && kv_norm && (Q == 0 || (cq && q_norm)), "dli_latent_prep: null pointer");
+  DLI_CHECK_ARG(Q >= 0 && K > 0 && R >= 0 && R % 2 == 0 && (R == 0 || (cos_t && sin_t && table_len > 0)),
                 "dli_latent_prep: Q=%d K=%d R=%d (R even, with a rotation table)", Q, K, R);
   DLI_CHECK_ARG((reinterpret_cast<uintptr_t>(ent) & 15u) == 0, "dli_latent_prep: ent must be 16-byte aligned");
   DLI_CHECK_ARG(dt == 0 || dt == 1, "element type %d: 0 = bf16, 1 = float", dt);
   if (rows <= 0) return DLI_OK;
-  LatentPrep a{row_ent, ent, page_table, max_pages, page_size, Q, K, R, ldp, q_off, kv_off, q_norm, kv_norm, eps, cos_t, sin_t};
+  LatentPrep a{row_ent, ent, page_table, max_pages, page_size, Q, K, R, ldp, q_off, kv_off, q_norm, kv_norm, eps, cos_t, sin_t, halves};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dt == 0) DLI_LAUNCH("latent_prep", latent_prep_kernel<bf16>, dim3(rows), dim3(256), 0, s, (const bf16*)proj, (bf16*)cq, (bf16*)pool, a);
   else DLI_LAUNCH("latent_prep", latent_prep_kernel<float>, dim3(rows), dim3(256), 0, s, (const float*)proj, (float*)cq, (float*)pool, a);
@@ -233,8 +241,8 @@ int dli_latent_prep(const void* proj, void* cq, void* pool, const int32_t* row_e
 }
 
 int dli_latent_q_absorb(const void* q, const void* uk, float* qbuf, const int32_t* row_ent, const int32_t* ent,
-                        const float* cos_t, const float* sin_t, int rows, int H, int D, int R, int K, int dt,
-                        dli_stream_t stream) {
+                        const float* cos_t, const float* sin_t, int rows, int H, int D, int R, int K, int halves, int ldq,
+                        int dt, dli_stream_t stream) {
   DLI_CHECK_ARG(q && qbuf && row_ent && ent, "dli_latent_q_absorb: null pointer");
   DLI_CHECK_ARG(uk || K == D, "dli_latent_q_absorb: without an up-projection the output size is the query size");
   DLI_CHECK_ARG(H > 0 && D > 0 && K > 0 && R >= 0 && R % 2 == 0 && (R == 0 || (cos_t && sin_t)) &&
@@ -247,8 +255,8 @@ int dli_latent_q_absorb(const void* q, const void* uk, float* qbuf, const int32_
   // few rows (decode): a head's outputs are dealt to several CTAs so that the up-projection is read by many SMs
   const dim3 grid((rows + kLatRows - 1) / kLatRows, H, rows <= 16 ? (K + th - 1) / th : 1);
   const size_t smem = (size_t)kLatRows * D * sizeof(float);
-  if (dt == 0) DLI_LAUNCH("latent_q_absorb", latent_q_absorb_kernel<bf16>, grid, dim3(th), smem, s, (const bf16*)q, (const bf16*)uk, qbuf, row_ent, ent, cos_t, sin_t, rows, H, D, R, K);
-  else DLI_LAUNCH("latent_q_absorb", latent_q_absorb_kernel<float>, grid, dim3(th), smem, s, (const float*)q, (const float*)uk, qbuf, row_ent, ent, cos_t, sin_t, rows, H, D, R, K);
+  if (dt == 0) DLI_LAUNCH("latent_q_absorb", latent_q_absorb_kernel<bf16>, grid, dim3(th), smem, s, (const bf16*)q, (const bf16*)uk, qbuf, row_ent, ent, cos_t, sin_t, rows, H, D, R, K, halves, ldq ? ldq : H * (D + R));
+  else DLI_LAUNCH("latent_q_absorb", latent_q_absorb_kernel<float>, grid, dim3(th), smem, s, (const float*)q, (const float*)uk, qbuf, row_ent, ent, cos_t, sin_t, rows, H, D, R, K, halves, ldq ? ldq : H * (D + R));
   return DLI_OK;
 }
 

@@ -405,6 +405,90 @@ silu_mul_kernel(const E* __restrict__ gu, E* __restrict__ act, int F, int ld) {
   }
 }
 
+
+// x += y / sqrt(mean(y^2) + eps) * w with a weight PER CHANNEL (y == NULL: x stays), then he = E(x) when he is given:
+// the post-norm of a sublayer whose successor reads the residual stream itself, as a GEMM operand.
+template <typename E>
+__global__ void __launch_bounds__(1024)
+postnorm_vec_add_kernel(const E* __restrict__ y, float* __restrict__ x, const float* __restrict__ w, E* __restrict__ he,
+                        int d, float eps) {
+  __shared__ float red[32];
+  pdl_wait();
+  pdl_trigger();
+  const size_t o = (size_t)blockIdx.x * d;
+  float r = 0.f;
+  if (y) {
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < d; c += blockDim.x) { const float v = to_f(y[o + c]); ss += v * v; }
+    ss = block_sum(ss, red);
+    r = 1.f / sqrtf(ss / d + eps);
+  }
+  for (int c = threadIdx.x; c < d; c += blockDim.x) {
+    float v = x[o + c];
+    if (y) { v += to_f(y[o + c]) * r * w[c]; x[o + c] = v; }
+    if (he) he[o + c] = from_f<E>(v);
+  }
+}
+
+// Per-layer token input, first half: g[row, c] = gelu_tanh(s[row, c]) * table[ids[row], off + c].
+template <typename E>
+__global__ void __launch_bounds__(256)
+token_side_act_kernel(const E* __restrict__ s, const int32_t* __restrict__ ids, const E* __restrict__ table,
+                      E* __restrict__ g, int n, int ld_tab, int off, int vocab) {
+  pdl_wait();
+  pdl_trigger();
+  const size_t row = blockIdx.x;
+  int id = ids[row];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+  for (int c = threadIdx.x; c < n; c += blockDim.x)
+    g[row * n + c] = from_f<E>(gelu_new_f(to_f(s[row * n + c])) * to_f(table[(size_t)id * ld_tab + off + c]));
+}
+
+// The whole per-layer token input for few rows (decode): y = Wp (gelu_tanh(Wg x) * table[id, off : off + n]),
+// x += y / sqrt(mean(y^2) + eps) * w, he = E(x).  One CTA per row; the row, the n gate values and y stay in shared
+// memory, products and sums are fp32.
+template <typename E>
+__global__ void __launch_bounds__(1024)
+token_side_kernel(float* __restrict__ x, const int32_t* __restrict__ ids, const E* __restrict__ table,
+                  const E* __restrict__ wg, const E* __restrict__ wp, const float* __restrict__ w, E* __restrict__ he,
+                  int d, int n, int ld_tab, int off, int vocab, float eps) {
+  extern __shared__ float sm_side[];
+  float* xs = sm_side;       // [d]
+  float* ys = xs + d;        // [d]
+  float* gs = ys + d;        // [n]
+  __shared__ float red[32];
+  pdl_wait();
+  pdl_trigger();
+  const size_t o = (size_t)blockIdx.x * d;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  int id = ids[blockIdx.x];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+  for (int c = threadIdx.x; c < d; c += blockDim.x) xs[c] = x[o + c];
+  __syncthreads();
+  for (int c = warp; c < n; c += nw) {
+    const E* wr = wg + (size_t)c * d;
+    float acc = 0.f;
+    for (int k = lane; k < d; k += 32) acc = fmaf(to_f(wr[k]), xs[k], acc);
+    acc = warp_sum(acc);
+    if (lane == 0) gs[c] = gelu_new_f(acc) * to_f(table[(size_t)id * ld_tab + off + c]);
+  }
+  __syncthreads();
+  float ss = 0.f;
+  for (int k = threadIdx.x; k < d; k += blockDim.x) {
+    const E* wr = wp + (size_t)k * n;
+    float acc = 0.f;
+    for (int c = 0; c < n; ++c) acc = fmaf(to_f(wr[c]), gs[c], acc);
+    ys[k] = acc;
+    ss = fmaf(acc, acc, ss);
+  }
+  ss = block_sum(ss, red);
+  const float r = 1.f / sqrtf(ss / d + eps);
+  for (int k = threadIdx.x; k < d; k += blockDim.x) {
+    const float v = xs[k] + ys[k] * r * w[k];
+    x[o + k] = v;
+    if (he) he[o + k] = from_f<E>(v);
+  }
+}
 }  // namespace dli
 
 using namespace dli;
@@ -568,6 +652,44 @@ int dli_silu_mul(const void* gu, void* act, int M, int F, int ld, int dt, dli_st
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (dt == 0) DLI_LAUNCH("silu_mul", silu_mul_kernel<bf16>, dim3(M), dim3(256), 0, s, (const bf16*)gu, (bf16*)act, F, ld);
   else DLI_LAUNCH("silu_mul", silu_mul_kernel<float>, dim3(M), dim3(256), 0, s, (const float*)gu, (float*)act, F, ld);
+  return DLI_OK;
+}
+
+int dli_postnorm_vec_add(const void* y, float* x, const float* w, void* he, int rows, int d, float eps, int dt,
+                         dli_stream_t stream) {
+  DLI_CHECK_ARG(x && d > 0 && (y == nullptr || w) && (y || he), "dli_postnorm_vec_add: null pointer or empty shape");
+  DT_CHECK(dt);
+  if (rows <= 0) return DLI_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dt == 0) DLI_LAUNCH("postnorm_vec_add", postnorm_vec_add_kernel<bf16>, dim3(rows), dim3(row_threads(rows, d)), 0, s, (const bf16*)y, x, w, (bf16*)he, d, eps);
+  else DLI_LAUNCH("postnorm_vec_add", postnorm_vec_add_kernel<float>, dim3(rows), dim3(row_threads(rows, d)), 0, s, (const float*)y, x, w, (float*)he, d, eps);
+  return DLI_OK;
+}
+
+int dli_token_side_act(const void* s_in, const int32_t* ids, const void* table, void* g, int rows, int n, int ld_tab, int off,
+                       int vocab, int dt, dli_stream_t stream) {
+  DLI_CHECK_ARG(s_in && ids && table && g && n > 0 && off >= 0 && off + n <= ld_tab && vocab > 0,
+                "dli_token_side_act: null pointer or bad shape");
+  DT_CHECK(dt);
+  if (rows <= 0) return DLI_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dt == 0) DLI_LAUNCH("token_side_act", token_side_act_kernel<bf16>, dim3(rows), dim3(n <= 128 ? 128 : 256), 0, s, (const bf16*)s_in, ids, (const bf16*)table, (bf16*)g, n, ld_tab, off, vocab);
+  else DLI_LAUNCH("token_side_act", token_side_act_kernel<float>, dim3(rows), dim3(n <= 128 ? 128 : 256), 0, s, (const float*)s_in, ids, (const float*)table, (float*)g, n, ld_tab, off, vocab);
+  return DLI_OK;
+}
+
+int dli_token_side(float* x, const int32_t* ids, const void* table, const void* w_gate, const void* w_proj, const float* w,
+                   void* he, int rows, int d, int n, int ld_tab, int off, int vocab, float eps, int dt, dli_stream_t stream) {
+  DLI_CHECK_ARG(x && ids && table && w_gate && w_proj && w && d > 0 && n > 0 && off >= 0 && off + n <= ld_tab && vocab > 0,
+                "dli_token_side: null pointer or bad shape");
+  const size_t smem = sizeof(float) * (2 * (size_t)d + n);
+  DLI_CHECK_ARG(smem <= 48 * 1024, "dli_token_side: width %d with %d side channels needs %zu bytes of shared memory", d, n, smem);
+  DT_CHECK(dt);
+  if (rows <= 0) return DLI_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int th = d >= 2048 ? 1024 : (d >= 512 ? 512 : 256);
+  if (dt == 0) DLI_LAUNCH("token_side", token_side_kernel<bf16>, dim3(rows), dim3(th), smem, s, x, ids, (const bf16*)table, (const bf16*)w_gate, (const bf16*)w_proj, w, (bf16*)he, d, n, ld_tab, off, vocab, eps);
+  else DLI_LAUNCH("token_side", token_side_kernel<float>, dim3(rows), dim3(th), smem, s, x, ids, (const float*)table, (const float*)w_gate, (const float*)w_proj, w, (float*)he, d, n, ld_tab, off, vocab, eps);
   return DLI_OK;
 }
 

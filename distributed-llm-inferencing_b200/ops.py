@@ -575,8 +575,9 @@ def attn_prep_append(proj, qbuf, k_cache, v_cache, row_ent, ent, page_table, H, 
 
 
 def attn_ragged(qbuf, k_cache, v_cache, proj, out, row_ent, ent, page_table, H, G, D, V, scale, chunk=0, window=0,
-                sink=None, g_off=-1, cos_v=None, sin_v=None, ldv=0, splits=1, part=None):
+                sink=None, g_off=-1, cos_v=None, sin_v=None, ldv=0, splits=1, part=None, first=0):
     """Chunk- / window-masked attention with an optional sink and output gate over the paged cache -> out [rows, H*V].
+    first: positions below it stay visible whatever the chunk or window says.
     ldv: elements between value rows (0 = V); v_cache may be k_cache itself (values = leading part of the keys).
     splits > 1: every row's keys are dealt to that many CTAs; part: float32 scratch of rows * H * splits * (V + 2)."""
     _f32(qbuf, sink, cos_v, sin_v, part), _i32(row_ent, ent, page_table), _req(out, k_cache.dtype), _req(proj, k_cache.dtype)
@@ -584,7 +585,7 @@ def attn_ragged(qbuf, k_cache, v_cache, proj, out, row_ent, ent, page_table, H, 
         raise ValueError("attn_ragged: scratch too small for the key splits")
     _call("dli_attn_ragged", 2 if splits > 1 else 1, _p(qbuf), _p(k_cache), _p(v_cache), _p(proj), _p(out), _p(row_ent), _p(ent),
           _p(page_table), page_table.shape[1], k_cache.shape[2], qbuf.shape[0], H, G, D, V, float(scale), int(chunk),
-          int(window), _p(sink), proj.shape[1] if proj is not None else 0, g_off, _p(cos_v), _p(sin_v), int(ldv),
+          int(window), int(first), _p(sink), proj.shape[1] if proj is not None else 0, g_off, _p(cos_v), _p(sin_v), int(ldv),
           int(splits), _p(part), _dt(k_cache), _stream())
     return out
 
@@ -594,7 +595,7 @@ def attn_ragged_tc_supported(D, V, dtype) -> bool:
 
 
 def attn_ragged_tc(qbuf, k_cache, v_cache, proj, out, ent, tiles, page_table, H, G, D, V, scale, chunk=0, window=0,
-                   sink=None, g_off=-1, cos_v=None, sin_v=None, page_base=0):
+                   sink=None, g_off=-1, cos_v=None, sin_v=None, page_base=0, first=0):
     """attn_ragged for steps with portions of prompts, on the tensor cores: tiles int32 [n_tiles, 2] = (entry, first
     row of the 64-row query tile within the entry).  page_base: k_cache / v_cache hold pages page_base.. of the pool only
     (the pages the step's sequences use must all lie in that range)."""
@@ -603,7 +604,7 @@ def attn_ragged_tc(qbuf, k_cache, v_cache, proj, out, ent, tiles, page_table, H,
     vb = page_base * v_cache.stride(0) * v_cache.element_size()
     _call("dli_attn_ragged_tc", 1, _p(qbuf), _p(k_cache) - kb, _p(v_cache) - vb, _p(proj), _p(out), _p(ent), _p(tiles),
           tiles.numel() // 2, _p(page_table), page_table.shape[1], k_cache.shape[2], H, G, D, V, float(scale), int(chunk),
-          int(window), _p(sink), proj.shape[1] if proj is not None else 0, g_off, _p(cos_v), _p(sin_v), _stream())
+          int(window), int(first), _p(sink), proj.shape[1] if proj is not None else 0, g_off, _p(cos_v), _p(sin_v), _stream())
     return out
 
 
@@ -650,22 +651,25 @@ def postnorm_add_norm_conv_single(y, x, tail, w, ent, out, g_post: float, g_next
 
 # ---------------------------------------------------------------------------------------------------------------
 # Latent attention, state-space mixer, mixture of experts (latent_attn.cu, mamba2.cu, moe.cu)
-def latent_prep(proj, cq, pool, row_ent, ent, page_table, Q, K, R, q_off, kv_off, q_norm, kv_norm, eps, cos_t, sin_t):
-    """Query latent (normed) -> cq [rows, Q]; key/value latent (normed) and the rotated shared key part -> the pool
-    [pages, 1, page_size, K + R]."""
+def latent_prep(proj, cq, pool, row_ent, ent, page_table, Q, K, R, q_off, kv_off, q_norm, kv_norm, eps, cos_t, sin_t,
+                halves=False):
+    """Query latent (normed) -> cq [rows, Q] (Q == 0: none); key/value latent (normed) and the rotated shared key part
+    -> the pool [pages, 1, page_size, K + R].  halves: rotation pairs (i, i + R/2) instead of (2i, 2i+1)."""
     _req(proj, proj.dtype), _req(cq, proj.dtype), _req(pool, proj.dtype)
     _f32(q_norm, kv_norm, cos_t, sin_t), _i32(row_ent, ent, page_table)
     _call("dli_latent_prep", 1, _p(proj), _p(cq), _p(pool), _p(row_ent), _p(ent), _p(page_table), page_table.shape[1],
           pool.shape[2], proj.shape[0], Q, K, R, proj.shape[1], q_off, kv_off, _p(q_norm), _p(kv_norm), float(eps),
-          _p(cos_t), _p(sin_t), cos_t.shape[0] if cos_t is not None else 0, _dt(proj), _stream())
+          _p(cos_t), _p(sin_t), cos_t.shape[0] if cos_t is not None else 0, int(bool(halves)), _dt(proj), _stream())
 
 
-def latent_q_absorb(q, uk, qbuf, row_ent, ent, cos_t, sin_t, H, D, R, K):
-    """q [rows, H*(D+R)], uk [H*D, K] -> qbuf float32 [rows, H*(K+R)] = per head [uk[h]^T q_n | rot(q_r)]; uk None
-    (K == D): [q_n | rot(q_r)]."""
-    _req(q, q.dtype), _req(uk, q.dtype), _f32(qbuf, cos_t, sin_t), _i32(row_ent, ent)
+def latent_q_absorb(q, uk, qbuf, row_ent, ent, cos_t, sin_t, H, D, R, K, halves=False):
+    """q [rows, H*(D+R)] (or the leading columns of a wider row-major matrix), uk [H*D, K] -> qbuf float32
+    [rows, H*(K+R)] = per head [uk[h]^T q_n | rot(q_r)]; uk None (K == D): [q_n | rot(q_r)]."""
+    if q.stride(1) != 1 or not q.is_cuda:
+        raise ValueError("latent_q_absorb: q needs unit inner stride on the device")
+    _req(uk, q.dtype), _f32(qbuf, cos_t, sin_t), _i32(row_ent, ent)
     _call("dli_latent_q_absorb", 1, _p(q), _p(uk), _p(qbuf), _p(row_ent), _p(ent), _p(cos_t), _p(sin_t), q.shape[0], H, D,
-          R, K, _dt(q), _stream())
+          R, K, int(bool(halves)), q.stride(0), _dt(q), _stream())
     return qbuf
 
 
@@ -758,3 +762,54 @@ def moe_sel(x, w_gu, w_down, sel_idx, sel_w, act_sel, y, n_exp, top, ff, limit, 
     _call("dli_moe_sel_bf16", 2, _p(x), _p(w_gu), _p(w_down), _p(sel_idx), _p(sel_w), _p(act_sel), _p(y), x.shape[0],
           x.shape[1], int(n_exp), int(top), int(ff), float(limit), int(ff_s), float(limit_s), float(alpha), _stream())
     return y
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Layers normed on their sublayers' outputs only, per-layer token input, gated delta rule (ragged_rows.cu, delta_rule.cu)
+def postnorm_vec_add(y, x, w, eps: float, he=None):
+    """x += y / rms(y) * w (x float32 in place, w float32 [d]; y None: x stays); he = x in its element type when given."""
+    _f32(x, w)
+    for t in (y, he):
+        if t is not None:
+            _req(t, t.dtype)
+    ref = y if y is not None else he
+    _call("dli_postnorm_vec_add", 1, _p(y), _p(x), _p(w), _p(he), x.shape[0], x.shape[1], float(eps), _dt(ref), _stream())
+    return x
+
+
+def token_side_act(s, ids, table, off: int, out):
+    """out [rows, n] = gelu_tanh(s) * table[ids, off : off + n]."""
+    _req(s, s.dtype), _req(table, s.dtype), _req(out, s.dtype), _i32(ids)
+    _call("dli_token_side_act", 1, _p(s), _p(ids), _p(table), _p(out), s.shape[0], s.shape[1], table.shape[1], int(off),
+          table.shape[0], _dt(s), _stream())
+    return out
+
+
+def token_side(x, ids, table, off: int, w_gate, w_proj, w, eps: float, he=None):
+    """Few rows: x += rmsnorm(w_proj (gelu_tanh(w_gate x) * table[ids, off : off + n])) * w in one kernel; he = x."""
+    _f32(x, w), _i32(ids), _req(table, table.dtype), _req(w_gate, table.dtype), _req(w_proj, table.dtype)
+    if he is not None:
+        _req(he, table.dtype)
+    _call("dli_token_side", 1, _p(x), _p(ids), _p(table), _p(w_gate), _p(w_proj), _p(w), _p(he), x.shape[0], x.shape[1],
+          w_gate.shape[0], table.shape[1], int(off), table.shape[0], float(eps), _dt(table), _stream())
+    return x
+
+
+def delta_rule_ragged(qkv, proj, St, o, ent, H, G, D, V, b_off, a_off, a_log, dt_bias, q_scale, unit_eps=1e-6):
+    """Gated delta rule over the rows of every entry.  qkv float32 [rows, 2*G*D + H*V] = q | k | v; St float32
+    [slots, H, V, D] (the transposed state) is advanced; o float32 [rows, H*V]."""
+    _f32(qkv, St, o, a_log, dt_bias), _req(proj, proj.dtype), _i32(ent)
+    _call("dli_delta_rule_ragged", 1, _p(qkv), _p(proj), _p(St), _p(o), _p(ent), ent.numel() // 4, H, G, D, V, qkv.shape[1],
+          proj.shape[1], b_off, a_off, _p(a_log), _p(dt_bias), float(q_scale), float(unit_eps), _dt(proj), _stream())
+    return o
+
+
+def head_rmsnorm_gate(o, proj, w, out, H, V, eps, gate=1, g_off=0):
+    """out [rows, H*V] = o / rms_head(o) * w * act(proj[:, g_off + h*V + v]); w float32 [V] (shared) or [H*V];
+    gate 0 none, 1 SiLU, 2 sigmoid."""
+    _f32(o, w), _req(out, out.dtype)
+    if proj is not None:
+        _req(proj, out.dtype)
+    _call("dli_head_rmsnorm_gate", 1, _p(o), _p(proj), _p(w), _p(out), o.shape[0], H, V, float(eps),
+          int(w.numel() == H * V and H > 1), int(gate), proj.shape[1] if proj is not None else 0, int(g_off), _dt(out), _stream())
+    return out

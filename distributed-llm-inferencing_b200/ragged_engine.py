@@ -33,7 +33,7 @@ BF = torch.bfloat16
 
 @dataclass
 class MixerSpec:
-    kind: str                      # "attention", "mlstm", "latent_attention" or "mamba2"
+    kind: str                      # "attention", "mlstm", "latent_attention", "mamba2" or "delta"
     heads: int
     kv_heads: int
     dim: int                       # query / key size per head
@@ -45,7 +45,8 @@ class MixerSpec:
     rot_scaling: Optional[dict] = None   # {factor, low, high, original}: wavelength-dependent frequency scaling
     chunk: int = 0                 # > 0: a position sees only its own block of `chunk` positions
     window: int = 0                # > 0: a position sees the last `window` positions
-    qk_norm: bool = False
+    keep_first: int = 0            # with a chunk or window: the first `keep_first` positions stay visible
+    qk_norm: bool = False          # per-head RMS norm of q and k (weights q_norm / k_norm; without them: plain division)
     rotate_values: bool = False    # values rotated by their position, outputs turned back by theirs
     sink: bool = False             # one extra softmax term per head without key or value
     head_gate: bool = False        # sigmoid gate per head on the output
@@ -54,13 +55,18 @@ class MixerSpec:
     # latent attention: queries and keys/values pass through low-rank latents; `dim` is the unrotated and `rot_dims`
     # the rotated query/key size per head; the cache holds kv_rank + rot_dims numbers per position
     kv_rank: int = 0
-    q_rank: int = 0
+    q_rank: int = 0                # 0: queries are projected directly, without a latent
     out_gate: bool = False         # sigmoid gate per output channel (head_gate: one per head)
+    rot_halves: bool = False       # rotation pairs (i, i + rot_dims/2) instead of interleaved (2i, 2i+1)
+    kv_from: Optional[int] = None  # the layer reads that (earlier) layer's cache and writes none of its own
     # mamba2: state rows per head, B/C groups, groups of the gated output norm, taps of the x/B/C convolution
     state: int = 0
     groups: int = 1
     norm_groups: int = 1
     conv_taps: int = 0
+    # delta (gated delta rule): heads value heads of size vdim, kv_heads query/key heads of size dim, conv_taps of the
+    # q / k / v convolution, scale on the unit queries, unit_eps under the root of the unit vectors
+    unit_eps: float = 1e-6
 
 
 @dataclass
@@ -91,6 +97,12 @@ class LayerSpec:
                                    # read it and x += mixer + feed-forward.  False: pre-/post-normed sublayers in sequence
     ckpt: Optional[int] = None     # the checkpoint's layer number when it differs from the position in `layers`
     reenter: Optional[int] = None  # t: before this layer x <- W_loop [x | embedding output] + step[t]
+    post_only: bool = False        # True: sublayers read x itself and x += rmsnorm(sublayer(x)) * weight vector; no input
+                                   # convolution
+    ff_limit: float = 0.0          # > 0: the dense feed-forward is min(g, limit) sigmoid(alpha min(g, limit)) (clamp(u) + 1)
+    ff_alpha: float = 1.702
+    side_dim: int = 0              # > 0: after the feed-forward, the per-layer token input of this size ...
+    side_off: int = 0              # ... read at this column of the side embedding table
 
 
 @dataclass
@@ -104,6 +116,7 @@ class HybridSpec:
     embed_scale: float = 1.0
     norm_groups: int = 0           # > 0: the final norm (and the norm of parallel layers) is grouped with a weight vector
     loop_passes: int = 0           # > 0: the model has the loop re-entry projection and per-pass vectors
+    side_width: int = 0            # > 0: columns of the side embedding table [vocab, side_width]
 
     @property
     def n_layers(self) -> int:
@@ -151,19 +164,29 @@ class RaggedEngine:
         torch.cuda.set_device(self.device)
         self.max_batch, self.max_seq_len = int(max_batch), int(max_seq_len)
         self.is_first = self.is_last = self.has_head = True
-        self.attn_layers = [i for i, L in enumerate(spec.layers) if L.mixer.kind in ("attention", "latent_attention")]
+        # layers that own a paged cache (a layer with kv_from reads its source's)
+        self.attn_layers = [i for i, L in enumerate(spec.layers)
+                            if L.mixer.kind in ("attention", "latent_attention") and L.mixer.kv_from is None]
         # latent attention caches ONE row [latent | rotated key part] per position and no values of its own
         shapes = [(1, m.kv_rank + m.rot_dims, 0) if m.kind == "latent_attention" else (m.kv_heads, m.dim, m.vdim)
                   for m in (spec.layers[i].mixer for i in self.attn_layers)]
         self.kv = PagedKVCache(len(shapes), 0, 0, page_size, self.max_batch, self.max_seq_len, self.device,
                                pool_tokens=kv_pool_tokens, layer_shapes=shapes, dtype=dtype)
         self.kv_index = {li: n for n, li in enumerate(self.attn_layers)}
+        for i, L in enumerate(spec.layers):
+            if L.mixer.kv_from is not None:
+                self.kv_index[i] = self.kv_index[L.mixer.kv_from]
         self.slots = StateSlots(self.max_batch, self.device)
         for i, L in enumerate(spec.layers):
-            if spec.taps > 1:
+            if spec.taps > 1 and not L.post_only:
                 self.slots.add(("tail1", i), spec.taps - 1, spec.width)
                 if L.ff:
                     self.slots.add(("tail2", i), spec.taps - 1, spec.width)
+            if L.mixer.kind == "delta":
+                m = L.mixer
+                self.slots.add(("S", i), m.heads, m.vdim, m.dim)  # value-major: the transposed state
+                if m.conv_taps > 1:
+                    self.slots.add(("ctail", i), m.conv_taps - 1, 2 * m.kv_heads * m.dim + m.heads * m.vdim)
             if L.mixer.kind == "mlstm":
                 m = L.mixer
                 self.slots.add(("S", i), m.heads, m.dim, m.vdim)
@@ -189,6 +212,7 @@ class RaggedEngine:
         self.moe_sel_max_rows = 8                  # up to this many rows a step reads only the chosen experts' weights ...
         self.moe_sel_share = 3.0                   # ... if they are at most 1/3 of all expert weights: the dense weight stream runs
                                                    # at ~0.63 of the HBM peak, the gathered one at ~0.2 (measured, 2048-wide)
+        self.side_fused_max_rows = 16              # up to this many rows the per-layer token input is one kernel
         self.latent_expand_max_elems = 1 << 31     # scratch bound (4 GiB in bf16) of the per-head expansion of cached latents
         self.mlstm_parallel_max_floats = 1 << 28   # scratch bound (1 GiB) of the block-parallel mLSTM / state-space scan; beyond it: blocks in order
         self.layer_trace: Optional[list] = None    # set to [] to collect the residual stream after every layer
@@ -228,14 +252,16 @@ class RaggedEngine:
 
         self.w = {"embed": t["embed"].to(E).contiguous().to(dev), "head": mat(t["head"]),
                   "final_norm": vec(t["final_norm"]) if s.norm_groups else float(t["final_norm"])}
+        if s.side_width:
+            self.w["side_embed"] = t["side_embed"].to(E).contiguous().to(dev)
         if s.loop_passes:
             self.w["loop_in"] = mat(t["loop_in"], pad_rows=False)
             self.w["loop_step"] = f32(t["loop_step"])
         self.layers = {}
         for i, src in t["layers"].items():
             L, m = s.layers[i], s.layers[i].mixer
-            d = {"canon1": f32(src["canon1"])}
-            if L.parallel:
+            d = {} if L.post_only else {"canon1": f32(src["canon1"])}
+            if L.parallel or L.post_only:
                 d["norm1"] = vec(src["norm1"])
             else:
                 d["norm1"], d["norm1b"] = float(src["norm1"]), float(src["norm1b"])
@@ -243,8 +269,10 @@ class RaggedEngine:
             if m.kind == "attention":
                 d["w_proj"] = mat(src["q"], src["k"], src["v"], src["g"]) if m.head_gate else mat(src["q"], src["k"], src["v"])
                 d["off"] = {"q": 0, "k": qn, "v": qn + kn, "g": qn + kn + vn if m.head_gate else -1}
-                d["q_norm"] = vec(src["q_norm"]) if m.qk_norm else None
-                d["k_norm"] = vec(src["k_norm"]) if m.qk_norm else None
+                # a norm without weights is the norm with unit weights
+                ones = torch.ones(m.dim, dtype=torch.float32, device=dev)
+                d["q_norm"] = (vec(src["q_norm"]) if "q_norm" in src else ones) if m.qk_norm else None
+                d["k_norm"] = (vec(src["k_norm"]) if "k_norm" in src else ones) if m.qk_norm else None
                 d["sink"] = vec(src["sink"]) if m.sink else None
             elif m.kind == "mlstm":
                 gn = m.heads * m.vdim
@@ -253,12 +281,22 @@ class RaggedEngine:
                             "f": 2 * qn + 2 * gn + m.heads}
                 d["i_b"], d["f_b"], d["out_norm"] = vec(src["i_b"]), vec(src["f_b"]), vec(src["out_norm"])
             elif m.kind == "latent_attention":
-                # one projection of the mixer's input: query latent | key/value latent and rotated key part | output gate
-                d["w_proj"] = mat(src["dq"], src["dkv"], src["g"]) if m.out_gate else mat(src["dq"], src["dkv"])
-                d["off"] = {"cq": 0, "kv": m.q_rank, "g": m.q_rank + m.kv_rank + m.rot_dims if m.out_gate else -1}
-                d["w_uq"] = mat(src["uq"], pad_rows=False)
+                # one projection of the mixer's input: query latent (or, without one, the queries themselves) | key/value
+                # latent and rotated key part (none in a layer that reads another layer's cache) | output gate
+                if m.kv_from is not None and m.q_rank:
+                    raise ValueError(f"layer {i}: a query latent together with another layer's cache is not supported")
+                nq = m.q_rank if m.q_rank else m.heads * (m.dim + m.rot_dims)
+                parts = [src["dq"] if m.q_rank else src["q"]] + ([src["dkv"]] if m.kv_from is None else []) + \
+                        ([src["g"]] if m.out_gate else [])
+                d["w_proj"] = mat(*parts)
+                nkv = m.kv_rank + m.rot_dims if m.kv_from is None else 0
+                d["off"] = {"cq": 0, "kv": nq, "g": nq + nkv if m.out_gate else -1}
+                if m.q_rank:
+                    d["w_uq"] = mat(src["uq"], pad_rows=False)
+                    d["q_norm"] = vec(src["dq_norm"])
+                d["kv_norm"] = vec(src["dkv_norm"]) if m.kv_from is None else None
+                d["sink"] = vec(src["sink"]) if m.sink else None
                 d["uk"], d["uv"] = mat(src["uk"], pad_rows=False), mat(src["uv"], pad_rows=False)
-                d["q_norm"], d["kv_norm"] = vec(src["dq_norm"]), vec(src["dkv_norm"])
                 if E == BF and ops.attn_ragged_tc_supported(m.dim + m.rot_dims, m.vdim, E):
                     # steps with portions of prompts expand the cached latents to per-head keys and values with ONE GEMM
                     # over the pool rows [latent | rotated key part]: [uk; uv] with zero columns under the rotated part
@@ -272,10 +310,23 @@ class RaggedEngine:
                 d["conv_w"], d["conv_b"] = f32(src["conv"]), vec(src["conv_b"])
                 d["dt_bias"], d["a_log"], d["d_skip"] = vec(src["dt_bias"]), vec(src["A_log"]), vec(src["D"])
                 d["out_norm"] = vec(src["out_norm"])
+            elif m.kind == "delta":
+                gd, hv = m.kv_heads * m.dim, m.heads * m.vdim
+                d["w_proj"] = mat(src["q"], src["k"], src["v"], src["g"], src["b"], src["a"])
+                d["off"] = {"q": 0, "k": gd, "v": 2 * gd, "g": 2 * gd + hv, "b": 2 * gd + 2 * hv, "a": 2 * gd + 2 * hv + m.heads}
+                d["conv_w"] = f32(src["conv"])
+                d["a_log"], d["dt_bias"], d["out_norm"] = vec(src["A_log"]), vec(src["dt_bias"]), vec(src["out_norm"])
             else:
                 raise ValueError(f"layer {i}: mixer kind {m.kind!r}")
             d["wo"] = mat(src["o"], pad_rows=False)
-            if L.ff:
+            if L.side_dim:
+                d["side_gate"], d["side_proj"] = mat(src["side_gate"], pad_rows=False), mat(src["side_proj"], pad_rows=False)
+                d["side_norm"] = vec(src["side_norm"])
+            if L.ff and L.post_only:
+                d["norm2"] = vec(src["norm2"])
+                d["w_gu"] = mat(src["gate"], src["up"])  # [gate rows | up rows]: the clamped activation is its own kernel
+                d["w_down"] = mat(src["down"], pad_rows=False)
+            elif L.ff:
                 d["norm2"], d["norm2b"] = float(src["norm2"]), float(src["norm2b"])
                 d["canon2"] = f32(src["canon2"])
                 # the tensor-core path interleaves gate and up rows so that silu(gate) * up is the GEMM's epilogue
@@ -357,15 +408,21 @@ class RaggedEngine:
         self._gu = torch.empty(rows * max(2 * ff, n_gu, 1), dtype=E, device=dev)
         lat = [m for m in mx if m.kind == "latent_attention"]
         if lat:
-            self._cq = torch.empty(rows * max(m.q_rank for m in lat), dtype=E, device=dev)
+            self._cq = torch.empty(rows * max(max(m.q_rank for m in lat), 1), dtype=E, device=dev)
             self._q = torch.empty(rows * max(m.heads * (m.dim + m.rot_dims) for m in lat), dtype=E, device=dev)
             self._olat = torch.empty(rows * max(m.heads * m.kv_rank for m in lat), dtype=E, device=dev)
             # partial sums of the key splits of decode rows (rows * heads * splits <= 8 * SMs + rows * heads)
             self._apart = torch.empty((8 * self._sms + 16 * max(m.heads for m in lat)) * (max(m.kv_rank for m in lat) + 2),
                                       dtype=f32, device=dev)
-        ssm = [m for m in mx if m.kind == "mamba2"]
+        ssm = [m for m in mx if m.kind in ("mamba2", "delta")]
         if ssm:
-            self._xbc = torch.empty(rows * max(m.heads * m.vdim + 2 * m.groups * m.state for m in ssm), dtype=f32, device=dev)
+            # fp32 outputs of a recurrent mixer's short convolution (x | B | C, or q | k | v)
+            self._xbc = torch.empty(rows * max(m.heads * m.vdim + 2 * (m.groups * m.state if m.kind == "mamba2" else
+                                                                         m.kv_heads * m.dim) for m in ssm), dtype=f32, device=dev)
+        sides = [L.side_dim for L in s.layers if L.side_dim]
+        if sides:
+            self._sg = torch.empty(rows * max(sides), dtype=E, device=dev)
+            self._sa = torch.empty(rows * max(sides), dtype=E, device=dev)
         if any(L.parallel for L in s.layers):
             self._he = torch.empty(rows, s.width, dtype=E, device=dev)
             self._y2 = torch.empty(rows, s.width, dtype=E, device=dev)
@@ -385,7 +442,8 @@ class RaggedEngine:
     def _lin(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         """out = x @ w.T: the framework's bf16 projection (tcgen05 GEMM / weight-streaming GEMV) where its alignment
         rules hold, else the CUDA-core GEMM (float32 engines, odd shapes)."""
-        if self.dtype == BF and x.shape[1] % 8 == 0 and w.shape[0] % 8 == 0:
+        if self.dtype == BF and x.shape[1] % 8 == 0 and w.shape[0] % 8 == 0 and x.is_contiguous() and \
+                not (x.shape[0] > 16 and (x.shape[1] % 64 or w.shape[0] % 16)):  # those would run row by row on the GEMV
             if 2 < x.shape[0] <= 128 and x.shape[1] % 64 == 0 and w.shape[0] % 16 == 0:
                 # few rows (batched decode, short portions): the split-K weight stream on every SM, as the uniform
                 # stacks' batched decode does
@@ -556,6 +614,14 @@ class RaggedEngine:
                 if self.layer_trace is not None:
                     self.layer_trace.append(x.clone())
                 continue
+            if L.post_only:
+                if y_prev is not None:
+                    ops.postnorm_add_norm(y_prev, x, g_prev, s.eps)
+                    y_prev = None
+                self._post_only_layer(li, L, P, rows, n_ent, views, long_step, tiles, first=(li == 0))
+                if self.layer_trace is not None:
+                    self.layer_trace.append(x.clone())
+                continue
             enter_sublayer(y_prev, g_prev, P["norm1"], self.slots.tensors.get(("tail1", li)), P.get("canon1"))
             n_proj = P["w_proj"].shape[0]
             proj = self._proj[:rows * n_proj].view(rows, n_proj)
@@ -564,21 +630,7 @@ class RaggedEngine:
             mix = self._mix[:rows * n_mix].view(rows, n_mix)
             off = P["off"]
             if m.kind == "attention":
-                kc, vc = self.kv.k[self.kv_index[li]], self.kv.v[self.kv_index[li]]
-                cq, sq = self._table(m.rot_base, m.rot_dims, m.rot_scaling) if m.rot_dims else (None, None)
-                cv, sv = self._table(m.rot_base, m.vdim, None) if m.rotate_values else (None, None)
-                qbuf = self._qbuf[:rows * m.heads * m.dim].view(rows, m.heads * m.dim)
-                ops.attn_prep_append(proj, qbuf, kc, vc, d_rent, d_ent, pt, m.heads, m.kv_heads, m.dim, m.vdim,
-                                     m.rot_dims, off["q"], off["k"], off["v"], P["q_norm"], P["k_norm"], s.eps,
-                                     cq, sq, cv, sv)
-                if tiles and m.scale > 0 and ops.attn_ragged_tc_supported(m.dim, m.vdim, E):
-                    ops.attn_ragged_tc(qbuf, kc, vc, proj, mix, d_ent, d_tiles, pt, m.heads, m.kv_heads, m.dim, m.vdim,
-                                       m.scale, chunk=m.chunk, window=m.window, sink=P["sink"], g_off=off["g"],
-                                       cos_v=cv, sin_v=sv)
-                else:
-                    ops.attn_ragged(qbuf, kc, vc, proj, mix, d_rent, d_ent, pt, m.heads, m.kv_heads, m.dim, m.vdim,
-                                    m.scale, chunk=m.chunk, window=m.window, sink=P["sink"], g_off=off["g"], cos_v=cv,
-                                    sin_v=sv)
+                self._attention(li, m, P, proj, mix, rows, views, tiles)
             else:
                 oscr = self._oscr[:rows * n_mix]
                 n_tiles = d_tiles.numel() // 2
@@ -633,6 +685,100 @@ class RaggedEngine:
         logits = logits_out[:nw] if logits_out is not None else torch.empty(nw, vp, dtype=E, device=dev)
         self._lin(hw, self.w["head"], logits)
         return logits
+
+    # ------------------------------------------------------------------ layers normed on their sublayers' outputs only
+    def _operand(self, rows, refresh):
+        """The residual stream as a GEMM operand: x itself in a float32 engine, else its copy in the element type (kept
+        up to date by the kernels that change x; `refresh` makes it anew after a layer of another style)."""
+        x = self._x[:rows]
+        if self.dtype == torch.float32:
+            return x
+        hc = self._hc[:rows]
+        if refresh:
+            ops.postnorm_vec_add(None, x, None, self.spec.eps, he=hc)
+        return hc
+
+    def _post_only_layer(self, li, L, P, rows, n_ent, views, long_step, tiles, first):
+        """x += norm1(mixer(x)); x += norm2(ff(x)); x += side_norm(side_proj(gelu(side_gate x) * token's side embedding))."""
+        s, E = self.spec, self.dtype
+        d_tok, d_rent, d_ent, d_want, d_tiles = views
+        x, y = self._x[:rows], self._y[:rows]
+        he = None if E == torch.float32 else self._hc[:rows]
+        prev_same = li > 0 and s.layers[li - 1].post_only
+        h = self._operand(rows, refresh=not prev_same)
+        m = L.mixer
+        n_proj = P["w_proj"].shape[0]
+        proj = self._proj[:rows * n_proj].view(rows, n_proj)
+        self._lin(h, P["w_proj"], proj)
+        n_mix = m.heads * m.vdim
+        mix = self._mix[:rows * n_mix].view(rows, n_mix)
+        off = P["off"]
+        if m.kind == "attention":
+            self._attention(li, m, P, proj, mix, rows, views, tiles)
+        elif m.kind == "latent_attention":
+            self._latent_attention(li, m, P, proj, mix, rows, views, tiles)
+        elif m.kind == "delta":
+            self._delta(li, m, P, proj, mix, rows, views)
+        else:
+            raise ValueError(f"layer {li}: mixer {m.kind!r} has no output-normed form")
+        self._lin(mix, P["wo"], y)
+        ops.postnorm_vec_add(y, x, P["norm1"], s.eps, he=he)
+        if L.ff:
+            n_gu = P["w_gu"].shape[0]
+            gu = self._gu[:rows * n_gu].view(rows, n_gu)
+            self._lin(h, P["w_gu"], gu)
+            act = self._act[:rows * L.ff].view(rows, L.ff)
+            ops.moe_act(gu, None, act, 0, 0, 0.0, ff_s=L.ff, limit_s=L.ff_limit, alpha=L.ff_alpha)
+            self._lin(act, P["w_down"], y)
+            ops.postnorm_vec_add(y, x, P["norm2"], s.eps, he=he)
+        if L.side_dim:
+            n = L.side_dim
+            if rows <= self.side_fused_max_rows and (2 * s.width + n) * 4 <= 48 * 1024:
+                ops.token_side(x, d_tok, self.w["side_embed"], L.side_off, P["side_gate"], P["side_proj"], P["side_norm"],
+                               s.eps, he=he)
+            else:
+                sg = self._sg[:rows * n].view(rows, n)
+                sa = self._sa[:rows * n].view(rows, n)
+                self._lin(h, P["side_gate"], sg)
+                ops.token_side_act(sg, d_tok, self.w["side_embed"], L.side_off, sa)
+                self._lin(sa, P["side_proj"], y)
+                ops.postnorm_vec_add(y, x, P["side_norm"], s.eps, he=he)
+
+    def _attention(self, li, m, P, proj, mix, rows, views, tiles):
+        """Softmax attention over the layer's paged keys and values: prep (head norms, rotation, append), then the
+        tensor-core tiles for steps with portions of prompts where the sizes have one, else the row-wise kernel."""
+        s, E = self.spec, self.dtype
+        d_tok, d_rent, d_ent, d_want, d_tiles = views
+        off, pt = P["off"], self.kv.page_table
+        kc, vc = self.kv.k[self.kv_index[li]], self.kv.v[self.kv_index[li]]
+        cq, sq = self._table(m.rot_base, m.rot_dims, m.rot_scaling) if m.rot_dims else (None, None)
+        cv, sv = self._table(m.rot_base, m.vdim, None) if m.rotate_values else (None, None)
+        qbuf = self._qbuf[:rows * m.heads * m.dim].view(rows, m.heads * m.dim)
+        ops.attn_prep_append(proj, qbuf, kc, vc, d_rent, d_ent, pt, m.heads, m.kv_heads, m.dim, m.vdim,
+                             m.rot_dims, off["q"], off["k"], off["v"], P["q_norm"], P["k_norm"], s.eps,
+                             cq, sq, cv, sv)
+        if tiles and m.scale > 0 and ops.attn_ragged_tc_supported(m.dim, m.vdim, E):
+            ops.attn_ragged_tc(qbuf, kc, vc, proj, mix, d_ent, d_tiles, pt, m.heads, m.kv_heads, m.dim, m.vdim,
+                               m.scale, chunk=m.chunk, window=m.window, sink=P["sink"], g_off=off["g"],
+                               cos_v=cv, sin_v=sv, first=m.keep_first)
+        else:
+            ops.attn_ragged(qbuf, kc, vc, proj, mix, d_rent, d_ent, pt, m.heads, m.kv_heads, m.dim, m.vdim,
+                            m.scale, chunk=m.chunk, window=m.window, sink=P["sink"], g_off=off["g"], cos_v=cv,
+                            sin_v=sv, first=m.keep_first)
+
+    def _delta(self, li, m, P, proj, mix, rows, views):
+        """Gated delta rule: short convolutions and SiLU of q | k | v (fp32), the recurrence over the state slot, then
+        the per-head norm, weight and SiLU gate."""
+        d_tok, d_rent, d_ent, d_want, d_tiles = views
+        off = P["off"]
+        C = 2 * m.kv_heads * m.dim + m.heads * m.vdim
+        qkv = self._xbc[:rows * C].view(rows, C)
+        ops.conv1d_act_ragged(proj, self.slots.tensors.get(("ctail", li)), P["conv_w"], None, d_rent, d_ent, qkv, off["q"],
+                              act=1)
+        o = self._oscr[:rows * m.heads * m.vdim].view(rows, m.heads * m.vdim)
+        ops.delta_rule_ragged(qkv, proj, self.slots[("S", li)], o, d_ent, m.heads, m.kv_heads, m.dim, m.vdim, off["b"],
+                              off["a"], P["a_log"], P["dt_bias"], m.scale, m.unit_eps)
+        ops.head_rmsnorm_gate(o, proj, P["out_norm"], mix, m.heads, m.vdim, self.spec.eps, gate=1, g_off=off["g"])
 
     # ------------------------------------------------------------------ layers with side-by-side sublayers
     def _parallel_layer(self, li, L, P, rows, n_ent, views, long_step, tiles):
@@ -697,12 +843,18 @@ class RaggedEngine:
         pool = self.kv.k[self.kv_index[li]]
         K, R, H, D, V = m.kv_rank, m.rot_dims, m.heads, m.dim, m.vdim
         cos_t, sin_t = self._table(m.rot_base, R, None) if R else (None, None)
-        cq = self._cq[:rows * m.q_rank].view(rows, m.q_rank)
+        hv = m.rot_halves
+        cq = self._cq[:rows * m.q_rank].view(rows, m.q_rank) if m.q_rank else None
         off = P["off"]
-        ops.latent_prep(proj, cq, pool, d_rent, d_ent, self.kv.page_table, m.q_rank, K, R, off["cq"], off["kv"],
-                        P["q_norm"], P["kv_norm"], self.spec.eps, cos_t, sin_t)
-        q = self._q[:rows * H * (D + R)].view(rows, H * (D + R))
-        self._lin(cq, P["w_uq"], q)
+        if m.kv_from is None:
+            ops.latent_prep(proj, cq, pool, d_rent, d_ent, self.kv.page_table, m.q_rank, K, R, off["cq"], off["kv"],
+                            P.get("q_norm"), P["kv_norm"], self.spec.eps, cos_t, sin_t, halves=hv)
+        if m.q_rank:
+            q = self._q[:rows * H * (D + R)].view(rows, H * (D + R))
+            self._lin(cq, P["w_uq"], q)
+        else:
+            q = proj[:, :H * (D + R)]  # the queries are the leading columns of the projection
+        sink = P.get("sink")
         ps = self.kv.page_size
         if tiles and "w_ukv" in P and m.scale > 0 and self._step_pages is not None and (K + R) % 8 == 0:
             lo, hi = self._step_pages
@@ -718,21 +870,21 @@ class RaggedEngine:
                 self._lin(rows_pool, P["w_ukv"], kvx)
                 ops.latent_expand(kvx, rows_pool, kx, vx, H, D, R, V, K, ps)
                 qbuf = self._qbuf[:rows * H * (D + R)].view(rows, H * (D + R))
-                ops.latent_q_absorb(q, None, qbuf, d_rent, d_ent, cos_t, sin_t, H, D, R, D)
+                ops.latent_q_absorb(q, None, qbuf, d_rent, d_ent, cos_t, sin_t, H, D, R, D, halves=hv)
                 ops.attn_ragged_tc(qbuf, kx, vx, None, mix, d_ent, d_tiles, self.kv.page_table, H, H, D + R, V, m.scale,
-                                   page_base=lo)
+                                   page_base=lo, sink=sink)
                 if m.out_gate:
                     ops.sigmoid_gate(mix, proj, off["g"])
                 return
         qbuf = self._qbuf[:rows * H * (K + R)].view(rows, H * (K + R))
-        ops.latent_q_absorb(q, P["uk"], qbuf, d_rent, d_ent, cos_t, sin_t, H, D, R, K)
+        ops.latent_q_absorb(q, P["uk"], qbuf, d_rent, d_ent, cos_t, sin_t, H, D, R, K, halves=hv)
         olat = self._olat[:rows * H * K].view(rows, H * K)
         # few rows (decode): every row's keys go to several CTAs, so that a long context is read by the whole GPU; the
         # count depends on the rows alone (a replayed graph keeps it while the contexts grow)
         splits = max(1, min(32, (8 * self._sms) // (rows * H))) if rows <= 16 else 1
         part = self._apart if splits > 1 else None
         ops.attn_ragged(qbuf, pool, pool, None, olat, d_rent, d_ent, self.kv.page_table, H, 1, K + R, K, m.scale,
-                        ldv=K + R, splits=splits, part=part)
+                        ldv=K + R, splits=splits, part=part, sink=sink)
         ops.latent_v_up(olat, P["uv"], proj if m.out_gate else None, mix, H, V, K, g_off=off["g"])
 
     def _mamba2(self, li, m, P, proj, mix, rows, views, long_step=False):

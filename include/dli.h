@@ -445,7 +445,8 @@ int dli_silu_mul(const void* gu, void* act, int M, int F, int ld, int dt, dli_st
  * rotation of the first rd dims (interleaved pairs; cos_qk / sin_qk [table_len, rd/2] fp32), rotation of the values
  * over all V dims (cos_v / sin_v [table_len, V/2] or NULL), q -> qbuf [rows, H, D] fp32, k and v -> the paged caches
  * [pages, G, page_size, D] / [pages, G, page_size, V].  dli_attn_ragged: scores (q . k) * scale over the keys the
- * chunk mask (chunk > 0: same block of `chunk` positions) and the window (window > 0) leave, softmax with an optional
+ * chunk mask (chunk > 0: same block of `chunk` positions) and the window (window > 0) leave, plus the positions below
+ * `first` whatever those two say (a window that keeps the sequence's first tokens in view), softmax with an optional
  * sink term exp(sink[h]) in the denominator, output turned back by the row's position (cos_v / sin_v) and multiplied
  * by sigmoid(proj[row, g_off + h]) (g_off < 0: no gate) -> out [rows, H, V].  ldv: elements between the value rows of
  * consecutive positions (0 = V); with v_cache == k_cache and ldv = D the values are the first V entries of the keys.
@@ -458,8 +459,8 @@ int dli_attn_prep_append(const void* proj, float* qbuf, void* k_cache, void* v_c
                          const float* sin_v, int table_len, int dt, dli_stream_t stream);
 int dli_attn_ragged(const float* qbuf, const void* k_cache, const void* v_cache, const void* proj, void* out,
                     const int32_t* row_ent, const int32_t* ent, const int32_t* page_table, int max_pages, int page_size,
-                    int rows, int H, int G, int D, int V, float scale, int chunk, int window, const float* sink, int ldp,
-                    int g_off, const float* cos_v, const float* sin_v, int ldv, int splits, float* part, int dt,
+                    int rows, int H, int G, int D, int V, float scale, int chunk, int window, int first, const float* sink,
+                    int ldp, int g_off, const float* cos_v, const float* sin_v, int ldv, int splits, float* part, int dt,
                     dli_stream_t stream);
 
 /* The same attention for steps that hold portions of prompts, on the tensor cores (bf16 caches only): one CTA per
@@ -468,8 +469,8 @@ int dli_attn_ragged(const float* qbuf, const void* k_cache, const void* v_cache,
 int dli_attn_ragged_tc_supported(int D, int V, int dt);
 int dli_attn_ragged_tc(const float* qbuf, const void* k_cache, const void* v_cache, const void* proj, void* out,
                        const int32_t* ent, const int32_t* tiles, int n_tiles, const int32_t* page_table, int max_pages,
-                       int page_size, int H, int G, int D, int V, float scale, int chunk, int window, const float* sink,
-                       int ldp, int g_off, const float* cos_v, const float* sin_v, dli_stream_t stream);
+                       int page_size, int H, int G, int D, int V, float scale, int chunk, int window, int first,
+                       const float* sink, int ldp, int g_off, const float* cos_v, const float* sin_v, dli_stream_t stream);
 
 /* Matrix-memory recurrent layer (mLSTM, stabilised): q, k, v, gate pre-activations and the output gate are columns
  * of proj [rows, ldp]; state S [slots, H, D, V], n [slots, H, D], m [slots, H] fp32 is read and advanced (an entry
@@ -496,14 +497,17 @@ int dli_mlstm_ragged_parallel(const void* proj, float* o_scratch, void* y, const
  * -> cq [rows, Q]; c = rmsnorm(proj[kv_off : +K]) * kv_norm and k_r = rot(proj[kv_off + K : +R]) -> the pool.
  * dli_latent_q_absorb: q [rows, H, D + R] and uk [H*D, K] -> qbuf [rows, H, K + R] fp32 = [uk[h]^T q_n | rot(q_r)], so
  * that dli_attn_ragged over the pool (G = 1, key size K + R, value size K, ldv = K + R) gives each head's output in
- * the latent; dli_latent_v_up: out [rows, H*V] = (uv[h] o[row, h]) * sigmoid(proj[row, g_off + h*V + v]). */
+ * the latent; dli_latent_v_up: out [rows, H*V] = (uv[h] o[row, h]) * sigmoid(proj[row, g_off + h*V + v]).
+ * Q == 0: the model has no query latent and that part is skipped (cq, q_norm may be NULL).  halves: pair i of a
+ * rotated part is entries (2i, 2i+1) when 0, entries (i, i + R/2) otherwise.  ldq: elements between the rows of q
+ * (0 = H * (D + R)). */
 int dli_latent_prep(const void* proj, void* cq, void* pool, const int32_t* row_ent, const int32_t* ent,
                     const int32_t* page_table, int max_pages, int page_size, int rows, int Q, int K, int R, int ldp,
                     int q_off, int kv_off, const float* q_norm, const float* kv_norm, float eps, const float* cos_t,
-                    const float* sin_t, int table_len, int dt, dli_stream_t stream);
+                    const float* sin_t, int table_len, int halves, int dt, dli_stream_t stream);
 int dli_latent_q_absorb(const void* q, const void* uk, float* qbuf, const int32_t* row_ent, const int32_t* ent,
-                        const float* cos_t, const float* sin_t, int rows, int H, int D, int R, int K, int dt,
-                        dli_stream_t stream);
+                        const float* cos_t, const float* sin_t, int rows, int H, int D, int R, int K, int halves, int ldq,
+                        int dt, dli_stream_t stream);
 int dli_latent_v_up(const void* o, const void* uv, const void* proj, void* out, int rows, int H, int V, int K, int ldp,
                     int g_off, int dt, dli_stream_t stream);
 /* Steps with portions of prompts run latent attention head by head on the tensor cores instead: kv [n, H*D + H*V] =
@@ -554,6 +558,33 @@ int dli_moe_sel_supported(int d, int ff, int ff_s, int top);
 int dli_moe_sel_bf16(const void* x, const void* w_gu, const void* w_down, const int32_t* sel_idx, const float* sel_w,
                      void* act_sel, void* y, int rows, int d, int n_exp, int top, int ff, float limit, int ff_s,
                      float limit_s, float alpha, dli_stream_t stream);
+
+/* Layers whose sublayers read the residual stream itself and are normed on their OUTPUT only.
+ * dli_postnorm_vec_add: x += y / sqrt(mean(y^2) + eps) * w with w [d] fp32 (y == NULL: x stays), he (optional,
+ * element type) = x afterwards, the next sublayer's GEMM operand.
+ * Per-layer token input: table [vocab, ld_tab] holds every layer's n-wide part of a token's side embedding at column
+ * off; dli_token_side_act: g [rows, n] = gelu_tanh(s) * table[ids[row], off : off + n] (s = the gate projection of x);
+ * dli_token_side does the whole update for few rows in one kernel: y = w_proj (gelu_tanh(w_gate x) * table[..]),
+ * x += y / sqrt(mean(y^2) + eps) * w, he = x. */
+int dli_postnorm_vec_add(const void* y, float* x, const float* w, void* he, int rows, int d, float eps, int dt,
+                         dli_stream_t stream);
+int dli_token_side_act(const void* s, const int32_t* ids, const void* table, void* g, int rows, int n, int ld_tab, int off,
+                       int vocab, int dt, dli_stream_t stream);
+int dli_token_side(float* x, const int32_t* ids, const void* table, const void* w_gate, const void* w_proj, const float* w,
+                   void* he, int rows, int d, int n, int ld_tab, int off, int vocab, float eps, int dt, dli_stream_t stream);
+
+/* Gated delta rule.  qkv [rows, ldx] fp32 = q [G*D] | k [G*D] | v [H*V] (after their convolutions and activations);
+ * per value head h (query/key head h / (H/G)): q, k made unit vectors (x / sqrt(sum x^2 + unit_eps)), q times q_scale,
+ * beta = sigmoid(proj[row, b_off + h]), g = exp(-exp(a_log[h]) * softplus(proj[row, a_off + h] + dt_bias[h]));
+ * S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q -> o [rows, H*V] fp32.  St [slots, H, V, D] fp32 holds
+ * the transposed state per sequence slot, read and advanced (an entry at position 0 starts from zero).
+ * dli_head_rmsnorm_gate: out [rows, H*V] = o / sqrt(mean_head(o^2) + eps) * w * act(proj[row, g_off + h*V + v]); w is
+ * [H, V] (w_heads != 0) or [V] shared by the heads; gate 0 = none, 1 = SiLU, 2 = sigmoid. */
+int dli_delta_rule_ragged(const float* qkv, const void* proj, float* St, float* o, const int32_t* ent, int n_ent, int H,
+                          int G, int D, int V, int ldx, int ldp, int b_off, int a_off, const float* a_log,
+                          const float* dt_bias, float q_scale, float unit_eps, int dt, dli_stream_t stream);
+int dli_head_rmsnorm_gate(const float* o, const void* proj, const float* w, void* out, int rows, int H, int V, float eps,
+                          int w_heads, int gate, int ldp, int g_off, int dt, dli_stream_t stream);
 
 #ifdef __cplusplus
 }
