@@ -719,6 +719,178 @@ def togalorn_kernel_times(eng, spec, T, peaks):
 
 
 
+# ---------------------------------------------------------------------------------- Fubepel beside Sokevik
+def fubepel_config(width, heads, kv, hd, ff, layers, vocab, window=1024):
+    """The Fubepel design at the sizes of a Llama layer: latent attention (64 + 64 key dims per head, value size hd, a
+    512-wide cached latent), a gated delta-rule layer (heads/2 value heads of 2 hd over heads/2 query/key heads of hd:
+    the matrix memory of the mLSTM layer it is compared with), windowed attention that keeps 4 first tokens, and a latent
+    attention layer on the first layer's cache; every layer with the dense feed-forward and a 256-wide token input."""
+    lat = {"type": "latent_attention",
+           "mixer": {"heads": heads, "dim": hd // 2, "rot_dim": hd // 2, "vdim": hd, "kv_rank": 512, "scale": hd ** -0.5,
+                     "rot": {"base": 500000.0, "dims": hd // 2}}}
+    dlt = {"type": "delta", "mixer": {"heads": heads // 2, "kv_heads": heads // 2, "dim": hd, "vdim": 2 * hd, "conv": 4}}
+    att = {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv, "dim": hd, "vdim": hd, "scale": hd ** -0.5,
+                                          "mask": {"size": window, "keep_first": 4}}}
+    mlp = {"kind": "dense", "ff": ff, "limit": 7.0}
+    order = [lat, dlt, att, dict(lat, mixer=dict(lat["mixer"], kv_from=0))]
+    return {"architecture": "Fubepel", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+            "token_side": {"dim": 256}, "layers": [dict(order[i % 4], mlp=mlp) for i in range(layers)]}
+
+
+def run_fubepel_compare(args, peaks):
+    """Prefill and decode throughput of the Fubepel design beside the framework's closest model, the Sokevik design
+    (both on RaggedEngine: attention beside a matrix-memory recurrent layer, dense feed-forwards), at equal layer sizes
+    and depth, random weights, plus each kernel of the new mechanisms alone against its roofline.  One JSON line; the
+    default workload of this file is untouched."""
+    from dli_b200 import fubepel, sokevik
+    from dli_b200.ragged_engine import RaggedEngine
+
+    T, K, W = args.ctx, args.steps, args.warmup
+    out = {"metric": "fubepel_vs_sokevik", "unit": "tokens/s", "ctx": T, "steps": K, "warmup": W, "dtype": "bf16",
+           "data": "synthetic", "peaks": peaks, "sizes": {}}
+    names = args.hybrid_sizes.split(",")
+    if len(names) > 1:
+        import subprocess
+        for name in names:
+            cmd = [sys.executable, os.path.abspath(__file__), "--compare-fubepel", "--hybrid-sizes", name, "--steps", str(K),
+                   "--warmup", str(W), "--ctx", str(T), "--batch", str(args.batch), "--page-size", str(args.page_size)]
+            p = subprocess.run(cmd, capture_output=True, text=True, check=True)
+            out["sizes"].update(json.loads(p.stdout.strip().splitlines()[-1])["sizes"])
+        return out
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for name in names:
+        width, heads, kv, hd, ff, layers, vocab = HYBRID_SIZES[name]
+        mods = ((fubepel, fubepel_config(width, heads, kv, hd, ff, layers, vocab), "fubepel"),
+                (sokevik, hybrid_config(width, heads, kv, hd, ff, layers, vocab, chunk=T), "sokevik"))
+        res = {}
+        for mod, cfg, tag in mods:
+            spec = mod.spec_from_config(cfg)
+            eng = RaggedEngine(spec, max_batch=max(args.batch, 8), max_seq_len=T + K + W + 64, page_size=args.page_size)
+            eng.load_tensors(mod.model_tensors(spec, mod.random_state_dict(spec, seed=1, std=0.02, device="cuda")))
+            res.update(ragged_throughput(eng, vocab, T, K, W, args.batch, tag, flush))
+            res[f"{tag}_kernels"] = fubepel_kernel_times(eng, spec, T, peaks) if tag == "fubepel" else \
+                hybrid_kernel_times(eng, spec, T, peaks)
+            eng.unload()
+            del eng
+            torch.cuda.empty_cache()
+        out["sizes"][name] = res
+    return out
+
+
+def fubepel_kernel_times(eng, spec, T, peaks):
+    """Each kernel of the Fubepel mechanisms alone at the step sizes of the comparison: a T-token portion (prefill) and
+    one token after T (decode), against its algorithmic HBM bytes or FLOPs and the measured peaks."""
+    from dli_b200 import ops
+
+    dev, E, W = eng.device, eng.dtype, spec.width
+    li_l = next(i for i, L in enumerate(spec.layers) if L.mixer.kind == "latent_attention" and L.mixer.kv_from is None)
+    li_d = next(i for i, L in enumerate(spec.layers) if L.mixer.kind == "delta")
+    li_a = next(i for i, L in enumerate(spec.layers) if L.mixer.kind == "attention")
+    hbm, tc = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    res = {}
+
+    def timeit(fn, n=5, reps=10):
+        fn()
+        return statistics.median(ev_time_ms(lambda: [fn() for _ in range(reps)]) for _ in range(n)) / reps
+
+    def put(key, ms, byt=None, flops=None, fp32=None):
+        d = {"ms": round(ms, 4)}
+        if byt is not None:
+            d["of_hbm"] = round(byt / (ms / 1e3) / hbm, 3)
+        if flops is not None:
+            d["of_bf16_peak"] = round(flops / (ms / 1e3) / tc, 4)
+        if fp32 is not None:
+            d["tflops_fp32"] = round(fp32 / (ms / 1e3) / 1e12, 3)
+        res[key] = d
+
+    slot = eng.open_sequence()
+    eng.kv.reserve(slot, T + 1)
+    eng.kv.commit()
+    eb = 2
+    for tag, rows, start in (("prefill", T, 0), ("decode", 1, T)):
+        eng._workspace(rows)
+        row_ent = torch.zeros(rows, dtype=torch.int32, device=dev)
+        ent = torch.tensor([slot, 0, rows, start], dtype=torch.int32, device=dev)
+        tiles = torch.tensor([[0, q0] for q0 in range(0, rows, 64)], dtype=torch.int32, device=dev)
+        views = (row_ent, row_ent, ent, row_ent, tiles)
+        eng._step_pages = (min(eng.kv.owned[slot]), max(eng.kv.owned[slot]))
+        x = torch.randn(rows, W, device=dev)
+        he = torch.empty(rows, W, dtype=E, device=dev)
+        y1 = torch.randn(rows, W, device=dev).to(E)
+        P = eng.layers[li_l]
+        put(f"{tag}_postnorm_vec_add", timeit(lambda: ops.postnorm_vec_add(y1, x, P["norm1"], 1e-6, he=he)),
+            byt=rows * W * (eb + 8 + eb))
+        # per-layer token input
+        L = spec.layers[li_l]
+        n = L.side_dim
+        tok = torch.randint(0, spec.vocab, (rows,), dtype=torch.int32, device=dev)
+        if rows <= eng.side_fused_max_rows and 2 * W * n * eb <= eng.side_fused_max_bytes:
+            put(f"{tag}_token_side", timeit(lambda: ops.token_side(x, tok, eng.w["side_embed"], L.side_off, P["side_gate"],
+                                                                   P["side_proj"], P["side_norm"], 1e-6, he=he)),
+                byt=2 * W * n * eb)
+        else:
+            sg, sa = torch.empty(rows, n, dtype=E, device=dev), torch.empty(rows, n, dtype=E, device=dev)
+
+            def side():
+                eng._lin(he, P["side_gate"], sg)
+                ops.token_side_act(sg, tok, eng.w["side_embed"], L.side_off, sa)
+                eng._lin(sa, P["side_proj"], y1)
+                ops.postnorm_vec_add(y1, x, P["side_norm"], 1e-6, he=he)
+            put(f"{tag}_token_side_all", timeit(side, n=3, reps=3), flops=4 * rows * W * n)
+        # latent attention: everything between the input projection and the output projection
+        m = spec.layers[li_l].mixer
+        proj = (0.5 * torch.randn(rows, P["w_proj"].shape[0], device=dev)).to(E)
+        mix = torch.empty(rows, m.heads * m.vdim, dtype=E, device=dev)
+        ms = timeit(lambda: eng._latent_attention(li_l, m, P, proj, mix, rows, views, rows > 1), n=3, reps=3)
+        if rows > 1:
+            fl = 2 * (rows * rows // 2) * m.heads * (m.dim + m.rot_dims + m.vdim) + 2 * rows * m.kv_rank * m.heads * (m.dim + m.vdim)
+            put(f"{tag}_latent_attention_all", ms, flops=fl)
+        else:
+            put(f"{tag}_latent_attention_all", ms, byt=(start + 1) * (m.kv_rank + m.rot_dims) * eb + (P["uk"].numel() + P["uv"].numel()) * eb)
+        # windowed attention with kept first tokens
+        m, P = spec.layers[li_a].mixer, eng.layers[li_a]
+        proj = (0.5 * torch.randn(rows, P["w_proj"].shape[0], device=dev)).to(E)
+        mix = torch.empty(rows, m.heads * m.vdim, dtype=E, device=dev)
+        ms = timeit(lambda: eng._attention(li_a, m, P, proj, mix, rows, views, rows > 1), n=3, reps=3)
+        span = min(m.window, start + rows) if m.window else start + rows
+        if rows > 1:
+            pairs = sum(min(t + 1, m.window) if m.window else t + 1 for t in range(rows))
+            put(f"{tag}_window_attention_all", ms, flops=2 * pairs * m.heads * (m.dim + m.vdim))
+        else:
+            put(f"{tag}_window_attention_all", ms, byt=span * m.kv_heads * (m.dim + m.vdim) * eb)
+        # gated delta rule: convolution, recurrence, head norm and gate
+        m, P = spec.layers[li_d].mixer, eng.layers[li_d]
+        C = 2 * m.kv_heads * m.dim + m.heads * m.vdim
+        proj = (0.5 * torch.randn(rows, P["w_proj"].shape[0], device=dev)).to(E)
+        qkv = torch.empty(rows, C, device=dev)
+        o = torch.empty(rows, m.heads * m.vdim, device=dev)
+        mix = torch.empty(rows, m.heads * m.vdim, dtype=E, device=dev)
+        off = P["off"]
+        put(f"{tag}_delta_conv", timeit(lambda: ops.conv1d_act_ragged(proj, eng.slots[("ctail", li_d)], P["conv_w"], None, row_ent,
+                                                                      ent, qkv, off["q"])), byt=rows * C * (eb + 4))
+        ms = timeit(lambda: ops.delta_rule_ragged(qkv, proj, eng.slots[("S", li_d)], o, ent, m.heads, m.kv_heads, m.dim, m.vdim,
+                                                  off["b"], off["a"], P["a_log"], P["dt_bias"], m.scale, m.unit_eps), n=3, reps=3)
+        if rows > 1:
+            put(f"{tag}_delta_rule", ms, fp32=rows * m.heads * m.dim * m.vdim * 6)   # three multiply-adds per state entry and token
+        else:
+            put(f"{tag}_delta_rule", ms, byt=2 * m.heads * m.dim * m.vdim * 4)
+        put(f"{tag}_delta_head_norm_gate", timeit(lambda: ops.head_rmsnorm_gate(o, proj, P["out_norm"], mix, m.heads, m.vdim, 1e-6,
+                                                                                gate=1, g_off=off["g"])),
+            byt=rows * m.heads * m.vdim * (4 + 2 * eb))
+        # feed-forward: gate/up projection with the clamped activation in its epilogue, beside the two-kernel form
+        L, P = spec.layers[li_d], eng.layers[li_d]
+        act = torch.empty(rows, L.ff, dtype=E, device=dev)
+        if P["packed"]:
+            sk = eng._splitk() if 2 < rows <= 128 else None
+            ms = timeit(lambda: ops.linear_gated_act(he, P["w_gu"], P["ff_act"], sk, out=act), n=3, reps=3)
+            if rows > 1:
+                put(f"{tag}_ff_gate_up_act", ms, flops=4 * rows * W * L.ff)
+            else:
+                put(f"{tag}_ff_gate_up_act", ms, byt=2 * W * L.ff * eb)
+    eng.close_sequence(slot)
+    return res
+
+
 def hybrid_kernel_times(eng, spec, T, peaks):
     """Each kernel of the ragged path alone at the step sizes of the comparison: a T-token portion (prefill) and one
     token after T (decode), against its algorithmic HBM bytes (or FLOPs) and the measured peaks."""
@@ -856,6 +1028,8 @@ def main():
                     help="instead of the default workload: the layer-by-layer family beside the uniform stack at equal sizes")
     ap.add_argument("--compare-togalorn", action="store_true",
                     help="instead of the default workload: the Togalorn design beside the Sokevik design at equal sizes")
+    ap.add_argument("--compare-fubepel", action="store_true",
+                    help="instead of the default workload: the Fubepel design beside the Sokevik design at equal sizes")
     ap.add_argument("--hybrid-sizes", default="1b,8b")
     args = ap.parse_args()
 
@@ -878,6 +1052,10 @@ def main():
     if args.compare_togalorn:
         if rank == 0:
             print(json.dumps(run_togalorn_compare(args, peaks)), flush=True)
+        return
+    if args.compare_fubepel:
+        if rank == 0:
+            print(json.dumps(run_fubepel_compare(args, peaks)), flush=True)
         return
     if world > 1 or args.gpus > 1:
         from dli_b200.pipeline import run_pipeline_bench

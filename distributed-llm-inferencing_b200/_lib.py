@@ -59,6 +59,8 @@ SIGNATURES = {
     "dli_gemv_mma_gated_silu_bf16": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "dli_gemm_gated_silu_bf16": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "dli_linear_gated_silu_bf16": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
+    "dli_gemv_gated_act_bf16": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp]),
+    "dli_linear_gated_act_bf16": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _sz, _vp]),
     "dli_gemm_qkv_rope_append_bf16": (_i, [_vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _vp]),
     "dli_argmax_bf16": (_i, [_vp, _i, _vp, _i, _i, _vp]),
     "dli_argmax_candidate_bf16": (_i, [_vp, _i, _i, _vp, _i, _i, _vp]),
@@ -68,7 +70,7 @@ SIGNATURES = {
     "dli_gemv_argmax_bf16": (_i, [_vp, _vp, _f, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _sz, _vp]),
     "dli_sample_bf16": (_i, [_vp, _i, _vp, _i, _i, _f, _i, _f, _vp, _vp, _vp, _vp, _i, _vp]),
     "dli_decode_advance": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp]),
-    "dli_embedding_f32": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _vp]),
+    "dli_embedding_f32": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _vp]),
     "dli_group_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _vp]),
     "dli_group_rmsnorm_conv_single": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _i, _vp]),
     "dli_residual_add2": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
@@ -104,6 +106,7 @@ SIGNATURES = {
                                 _i, _vp, _vp, _vp]),
     "dli_postnorm_vec_add": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp]),
     "dli_token_side_act": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+    "dli_token_side_gate": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "dli_token_side": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp]),
     "dli_delta_rule_ragged": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _f, _f, _i, _vp]),
     "dli_head_rmsnorm_gate": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _i, _i, _i, _i, _vp]),

@@ -183,6 +183,15 @@ __device__ __forceinline__ uint4 pack8(const float* f) {
 // Activations, evaluated the way torch evaluates them on a bf16 tensor:
 // upcast to fp32, compute, round once to bf16 (the caller rounds).
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + expf(-x)); }
+// Epilogue of a gated projection pair.  act == NULL: silu(gate) * up with the rounding points of a bf16 framework.
+// act = {limit, alpha} (two floats on the device): the clamped form g * sigmoid(alpha g) * (u + 1) with
+// g = min(gate, limit), u = clamp(up, -limit, limit).
+__device__ __forceinline__ float gated_combine(float gte, float up, const float* __restrict__ act) {
+  if (act == nullptr) return round_bf16(silu_f(gte)) * up;
+  const float lim = act[0], alpha = act[1];
+  const float g = fminf(gte, lim), u = fminf(fmaxf(up, -lim), lim);
+  return g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+}
 // gelu_new (tanh approximation), TF:activations.py:59-66
 __device__ __forceinline__ float gelu_new_f(float x) {
   const float k = 0.7978845608028654f;  // sqrt(2/pi)

@@ -2,11 +2,12 @@
 // G query/key heads) the layer keeps a matrix S [D, V] per sequence:
 //   q_t, k_t  unit vectors (x / sqrt(sum x^2 + unit_eps)), q_t also times q_scale
 //   beta_t = sigmoid(b_t),  g_t = exp(-exp(A_log_h) * softplus(a_t + dt_bias_h))
-//   S <- g_t S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t      (the read-out sees the write)
+//   S <- g_t S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t      (the read-out sees the write:
+//   o_t = g_t S_(t-1)^T q_t + u (k_t . q_t), which is how the kernel evaluates it)
 // Column c of S (all D rows of one value dimension) never meets another column, so the recurrence is dealt to the
-// GPU by value column: a warp owns kDeltaCols columns with lane l holding rows l, l + 32, ... in registers, a CTA
-// owns 8 warps' columns of one (entry, head) and walks the entry's rows in order.  The rows' q, k (normalised once
-// per CTA), v, beta and g are staged in shared memory kDeltaBlock rows at a time.  The state is stored value-major,
+// GPU by value column: a column's D rows live in the registers of consecutive lanes (4 or 16 rows each), a thread
+// carries one or two columns, and a CTA of 4 warps walks the rows of one (entry, head) in order.  The rows' q, k (normalised
+// once per CTA), v, beta and g are staged in shared memory kDeltaBlock rows at a time.  The state is stored value-major,
 // S^T [slots, H, V, D], so that a warp reads and writes its columns as contiguous runs.
 //   dli_delta_rule_ragged   qkv fp32 [rows, 2*G*D + H*V] (q | k | v after their convolutions and activations),
 //                           b_t / a_t columns of the projection row -> o fp32 [rows, H*V]; state read and advanced
@@ -36,124 +37,199 @@ struct DeltaRun {
   float q_scale, unit_eps;
 };
 
-constexpr int kDeltaWarps = 8;
-constexpr int kDeltaCols = 2;    // value columns per warp
-constexpr int kDeltaBlock = 16;  // rows staged per pass
+constexpr int kDeltaWarps = 4;
+constexpr int kDeltaBlock = 16;  // rows of the step staged per pass
+// NS state rows per thread and column: 16 (a lane's 16 key entries start 20 floats apart, so that its 16-byte loads
+// meet no bank conflicts) or 4 (a warp's lanes read 512 consecutive bytes)
+__host__ __device__ constexpr int delta_pad(int NS) { return NS == 4 ? 4 : NS + 4; }
+constexpr int kDeltaPre = 4;     // a lane prefetches up to 4 query and 4 key entries of a row (key sizes up to 128)
 
-// Grid (entries, H, ceil(V / (kDeltaWarps * kDeltaCols))).  NS = ceil(D / 32) state rows per lane and column.
-template <typename E, int NS>
+// lanes that share a column: the smallest power of two with lanes * NS >= D
+__host__ __device__ inline int delta_lanes(int D, int NS) {
+  int l = 1;
+  while (l * NS < D) l <<= 1;
+  return l;
+}
+__host__ __device__ inline int delta_cols_per_cta(int D, int NS, int cpt) { return kDeltaWarps * (32 / delta_lanes(D, NS)) * cpt; }
+
+// Grid (entries, H, ceil(V / columns per CTA)).  A column's D state rows are dealt to `lanes` consecutive lanes, NS
+// consecutive rows each, so S^T k and S^T q need NS multiply-adds and log2(lanes) shuffles per lane; a thread carries
+// CPT columns.  The walk over the rows is one dependent chain per column, so its speed is set by how many warps a
+// scheduler can switch between: (NS, CPT) = (16, 2) does the work with the fewest instructions and is taken when
+// there are columns enough to fill the GPU with it, (16, 1) and (4, 1) spread the same columns over 2x and 8x as many
+// warps.  While a pass of 16 rows is computed, the next pass's raw q and k rows are already on their way
+// into registers (key sizes up to 128), so the recurrence does not wait for global memory between passes.
+template <typename E, int CPT, int NS>
 __global__ void __launch_bounds__(kDeltaWarps * 32)
 delta_rule_kernel(const float* __restrict__ qkv, const E* __restrict__ proj, float* __restrict__ St,
                   float* __restrict__ o, DeltaRun a) {
-  extern __shared__ float sm_delta[];
-  const int D = a.D;
-  float* qs = sm_delta;                                    // [kDeltaBlock][D]
-  float* ks = qs + kDeltaBlock * D;                        // [kDeltaBlock][D]
-  float* vs = ks + kDeltaBlock * D;                        // [kDeltaBlock][kDeltaWarps * kDeltaCols]
-  float* bg = vs + kDeltaBlock * kDeltaWarps * kDeltaCols; // [kDeltaBlock][2]: beta, g
+  extern __shared__ __align__(16) float sm_delta[];
+  constexpr int kDeltaRows = NS, kDeltaPad = delta_pad(NS);
+  const int D = a.D, lanes = delta_lanes(D, NS), ldk = lanes * kDeltaPad, cpb = delta_cols_per_cta(D, NS, CPT);
+  float* qs = sm_delta;                   // [kDeltaBlock][ldk]
+  float* ks = qs + kDeltaBlock * ldk;     // [kDeltaBlock][ldk]
+  float* vs = ks + kDeltaBlock * ldk;     // [kDeltaBlock][cpb]
+  float* bg = vs + kDeltaBlock * cpb;     // [kDeltaBlock][3]: beta, g, k . q of the unit vectors (q scaled)
   pdl_wait();
   pdl_trigger();
   const int4 e = reinterpret_cast<const int4*>(a.ent)[blockIdx.x];  // slot, first row, rows, first position
   const int h = blockIdx.y, gq = h / (a.H / a.G);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  constexpr int CPB = kDeltaWarps * kDeltaCols;
-  const int c0 = blockIdx.z * CPB + warp * kDeltaCols;
-  float s[kDeltaCols][NS];
+  const int p = lane % lanes, cg = lane / lanes;             // part of the column, column group within the warp
+  const int cl = (warp * (32 / lanes) + cg) * CPT;           // first of the thread's columns within the CTA
+  const int c0 = blockIdx.z * cpb + cl;
+  const int r0 = p * kDeltaRows;                             // the thread's first state row
+  float s[CPT][kDeltaRows];
 #pragma unroll
-  for (int c = 0; c < kDeltaCols; ++c) {
-    const float* sp = St + (((size_t)e.x * a.H + h) * a.V + (c0 + c)) * D;
+  for (int c = 0; c < CPT; ++c) {
+    const float* sp = St + (((size_t)e.x * a.H + h) * a.V + (c0 + c)) * D + r0;
 #pragma unroll
-    for (int n = 0; n < NS; ++n) {
-      const int i = lane + 32 * n;
-      s[c][n] = (e.w > 0 && c0 + c < a.V && i < D) ? sp[i] : 0.f;
-    }
+    for (int n = 0; n < kDeltaRows; ++n) s[c][n] = (e.w > 0 && c0 + c < a.V && r0 + n < D) ? sp[n] : 0.f;
   }
   const float neg_a = -expf(a.a_log[h]), dtb = a.dt_bias[h];
-  const int q_col = gq * D, k_col = a.G * D + gq * D, v_col = 2 * a.G * D + h * a.V + blockIdx.z * CPB;
+  const int q_col = gq * D, k_col = a.G * D + gq * D, v_col = 2 * a.G * D + h * a.V + blockIdx.z * cpb;
+  const bool pre = D <= 32 * kDeltaPre;
+  constexpr int TPW = kDeltaBlock / kDeltaWarps;             // rows of a pass that one warp normalises
+  float pq[TPW][kDeltaPre], pk[TPW][kDeltaPre];
+
+  // raw q and k entries of the warp's rows of the pass that starts at row t0 -> registers
+  auto fetch = [&](int t0) {
+    const int nt = min(kDeltaBlock, e.z - t0);
+#pragma unroll
+    for (int j = 0; j < TPW; ++j) {
+      const int t = warp + j * kDeltaWarps;
+      const float* xr = qkv + (size_t)(e.y + t0 + min(t, nt - 1)) * a.ldx;
+#pragma unroll
+      for (int n = 0; n < kDeltaPre; ++n) {
+        const int i = lane + 32 * n;
+        pq[j][n] = i < D ? xr[q_col + i] : 0.f;
+        pk[j][n] = i < D ? xr[k_col + i] : 0.f;
+      }
+    }
+  };
+  if (pre && e.z > 0) fetch(0);
 
   for (int t0 = 0; t0 < e.z; t0 += kDeltaBlock) {
     const int nt = min(kDeltaBlock, e.z - t0);
     __syncthreads();  // the previous pass has been consumed
-    // a warp normalises the queries and keys of rows warp, warp + 8, ...
-    for (int t = warp; t < nt; t += kDeltaWarps) {
-      const float* xr = qkv + (size_t)(e.y + t0 + t) * a.ldx;
-      float qv[NS], kv[NS], qq = 0.f, kk = 0.f;
+    // a warp normalises the queries and keys of rows warp, warp + 4, ...
+    if (pre) {
 #pragma unroll
-      for (int n = 0; n < NS; ++n) {
-        const int i = lane + 32 * n;
-        qv[n] = i < D ? xr[q_col + i] : 0.f;
-        kv[n] = i < D ? xr[k_col + i] : 0.f;
-        qq = fmaf(qv[n], qv[n], qq);
-        kk = fmaf(kv[n], kv[n], kk);
+      for (int j = 0; j < TPW; ++j) {
+        const int t = warp + j * kDeltaWarps;
+        float qq = 0.f, kk = 0.f, qk = 0.f;
+#pragma unroll
+        for (int n = 0; n < kDeltaPre; ++n) {
+          qq = fmaf(pq[j][n], pq[j][n], qq);
+          kk = fmaf(pk[j][n], pk[j][n], kk);
+          qk = fmaf(pq[j][n], pk[j][n], qk);
+        }
+        qq = a.q_scale / sqrtf(warp_sum(qq) + a.unit_eps);
+        kk = 1.f / sqrtf(warp_sum(kk) + a.unit_eps);
+        qk = warp_sum(qk) * qq * kk;
+        if (t < nt) {
+          if (lane == 0) bg[3 * t + 2] = qk;
+#pragma unroll
+          for (int n = 0; n < kDeltaPre; ++n) {
+            const int i = lane + 32 * n;
+            if (i < lanes * kDeltaRows) {
+              const int at = t * ldk + (i / kDeltaRows) * kDeltaPad + i % kDeltaRows;
+              qs[at] = pq[j][n] * qq;
+              ks[at] = pk[j][n] * kk;
+            }
+          }
+        }
       }
-      qq = a.q_scale / sqrtf(warp_sum(qq) + a.unit_eps);
-      kk = 1.f / sqrtf(warp_sum(kk) + a.unit_eps);
-#pragma unroll
-      for (int n = 0; n < NS; ++n) {
-        const int i = lane + 32 * n;
-        if (i < D) { qs[t * D + i] = qv[n] * qq; ks[t * D + i] = kv[n] * kk; }
+    } else {
+      for (int t = warp; t < nt; t += kDeltaWarps) {
+        const float* xr = qkv + (size_t)(e.y + t0 + t) * a.ldx;
+        float qq = 0.f, kk = 0.f, qk = 0.f;
+        for (int i = lane; i < D; i += 32) {
+          const float qv = xr[q_col + i], kv = xr[k_col + i];
+          qq = fmaf(qv, qv, qq);
+          kk = fmaf(kv, kv, kk);
+          qk = fmaf(qv, kv, qk);
+        }
+        qq = a.q_scale / sqrtf(warp_sum(qq) + a.unit_eps);
+        kk = 1.f / sqrtf(warp_sum(kk) + a.unit_eps);
+        qk = warp_sum(qk) * qq * kk;
+        if (lane == 0) bg[3 * t + 2] = qk;
+        for (int i = lane; i < lanes * kDeltaRows; i += 32) {
+          const int at = t * ldk + (i / kDeltaRows) * kDeltaPad + i % kDeltaRows;
+          qs[at] = i < D ? xr[q_col + i] * qq : 0.f;
+          ks[at] = i < D ? xr[k_col + i] * kk : 0.f;
+        }
       }
     }
-    for (int i = tid; i < nt * CPB; i += kDeltaWarps * 32) {
-      const int t = i / CPB, c = i - t * CPB;
-      vs[i] = (blockIdx.z * CPB + c < a.V) ? qkv[(size_t)(e.y + t0 + t) * a.ldx + v_col + c] : 0.f;
+    for (int i = tid; i < nt * cpb; i += kDeltaWarps * 32) {
+      const int t = i / cpb, c = i - t * cpb;
+      vs[i] = (blockIdx.z * cpb + c < a.V) ? qkv[(size_t)(e.y + t0 + t) * a.ldx + v_col + c] : 0.f;
     }
     if (tid < nt) {
       const E* pr = proj + (size_t)(e.y + t0 + tid) * a.ldp;
       const float b = d_to_f(pr[a.b_off + h]), x = d_to_f(pr[a.a_off + h]) + dtb;
       const float sp = x > 20.f ? x : log1pf(expf(x));
-      bg[2 * tid] = 1.f / (1.f + expf(-b));
-      bg[2 * tid + 1] = expf(neg_a * sp);
+      bg[3 * tid] = 1.f / (1.f + expf(-b));
+      bg[3 * tid + 1] = expf(neg_a * sp);
     }
     __syncthreads();
+    if (pre && t0 + kDeltaBlock < e.z) fetch(t0 + kDeltaBlock);   // in flight while this pass is computed
     for (int t = 0; t < nt; ++t) {
-      float kk[NS], qq[NS];
+      float kk[kDeltaRows], qq[kDeltaRows];
+      const float4* kp = reinterpret_cast<const float4*>(ks + t * ldk + p * kDeltaPad);
+      const float4* qp = reinterpret_cast<const float4*>(qs + t * ldk + p * kDeltaPad);
 #pragma unroll
-      for (int n = 0; n < NS; ++n) {
-        const int i = lane + 32 * n;
-        kk[n] = i < D ? ks[t * D + i] : 0.f;
-        qq[n] = i < D ? qs[t * D + i] : 0.f;
+      for (int n = 0; n < kDeltaRows / 4; ++n) {
+        const float4 kf = kp[n], qf = qp[n];
+        kk[4 * n] = kf.x; kk[4 * n + 1] = kf.y; kk[4 * n + 2] = kf.z; kk[4 * n + 3] = kf.w;
+        qq[4 * n] = qf.x; qq[4 * n + 1] = qf.y; qq[4 * n + 2] = qf.z; qq[4 * n + 3] = qf.w;
       }
-      const float beta = bg[2 * t], g = bg[2 * t + 1];
-      float r[kDeltaCols];
+      const float beta = bg[3 * t], g = bg[3 * t + 1], kq = bg[3 * t + 2];
+      // both read-outs come from the state BEFORE this row's write: S_old^T k for the write itself and S_old^T q for the
+      // output, o = g S_old^T q + u (k . q); the two reductions run side by side and only the first one is on the path
+      // to the next row
+      float ra[CPT], rb[CPT];
 #pragma unroll
-      for (int c = 0; c < kDeltaCols; ++c) {
-        r[c] = 0.f;
+      for (int c = 0; c < CPT; ++c) {
+        float a4[4] = {0.f, 0.f, 0.f, 0.f}, b4[4] = {0.f, 0.f, 0.f, 0.f};   // partial sums: chains of NS / 4 multiply-adds
 #pragma unroll
-        for (int n = 0; n < NS; ++n) r[c] = fmaf(s[c][n], kk[n], r[c]);
+        for (int n = 0; n < kDeltaRows; ++n) {
+          a4[n & 3] = fmaf(s[c][n], kk[n], a4[n & 3]);
+          b4[n & 3] = fmaf(s[c][n], qq[n], b4[n & 3]);
+        }
+        ra[c] = (a4[0] + a4[1]) + (a4[2] + a4[3]);
+        rb[c] = (b4[0] + b4[1]) + (b4[2] + b4[3]);
       }
+      for (int off = 1; off < lanes; off <<= 1) {
 #pragma unroll
-      for (int c = 0; c < kDeltaCols; ++c) r[c] = warp_sum(r[c]);
-      float ov[kDeltaCols];
-#pragma unroll
-      for (int c = 0; c < kDeltaCols; ++c) {
-        const float u = beta * (vs[t * CPB + warp * kDeltaCols + c] - g * r[c]);
-        ov[c] = 0.f;
-#pragma unroll
-        for (int n = 0; n < NS; ++n) {
-          s[c][n] = fmaf(g, s[c][n], kk[n] * u);
-          ov[c] = fmaf(s[c][n], qq[n], ov[c]);
+        for (int c = 0; c < CPT; ++c) {
+          ra[c] += __shfl_xor_sync(0xffffffffu, ra[c], off);
+          rb[c] += __shfl_xor_sync(0xffffffffu, rb[c], off);
         }
       }
+      float ov[CPT];
 #pragma unroll
-      for (int c = 0; c < kDeltaCols; ++c) ov[c] = warp_sum(ov[c]);
-      if (lane < kDeltaCols && c0 + lane < a.V) {
-        float val = ov[0];
+      for (int c = 0; c < CPT; ++c) {
+        const float u = beta * (vs[t * cpb + cl + c] - g * ra[c]);
+        ov[c] = fmaf(g, rb[c], u * kq);
 #pragma unroll
-        for (int c = 1; c < kDeltaCols; ++c) if (lane == c) val = ov[c];
-        o[(size_t)(e.y + t0 + t) * (a.H * a.V) + h * a.V + c0 + lane] = val;
+        for (int n = 0; n < kDeltaRows; ++n) s[c][n] = fmaf(g, s[c][n], kk[n] * u);
+      }
+      if (p == 0) {
+        float* orow = o + (size_t)(e.y + t0 + t) * (a.H * a.V) + h * a.V + c0;
+#pragma unroll
+        for (int c = 0; c < CPT; ++c)
+          if (c0 + c < a.V) orow[c] = ov[c];
       }
     }
   }
 #pragma unroll
-  for (int c = 0; c < kDeltaCols; ++c) {
+  for (int c = 0; c < CPT; ++c) {
     if (c0 + c >= a.V) continue;
-    float* sp = St + (((size_t)e.x * a.H + h) * a.V + (c0 + c)) * D;
+    float* sp = St + (((size_t)e.x * a.H + h) * a.V + (c0 + c)) * D + r0;
 #pragma unroll
-    for (int n = 0; n < NS; ++n) {
-      const int i = lane + 32 * n;
-      if (i < D) sp[i] = s[c][n];
-    }
+    for (int n = 0; n < kDeltaRows; ++n)
+      if (r0 + n < D) sp[n] = s[c][n];
   }
 }
 
@@ -185,22 +261,29 @@ head_rmsnorm_gate_kernel(const float* __restrict__ o, const E* __restrict__ proj
   }
 }
 
-template <typename E, int NS>
+template <typename E, int CPT, int NS>
 static int launch_delta(const float* qkv, const void* proj, float* St, float* o, int n_ent, const DeltaRun& a,
                         cudaStream_t s) {
-  const size_t smem = sizeof(float) * ((size_t)2 * kDeltaBlock * a.D + kDeltaBlock * kDeltaWarps * kDeltaCols + 2 * kDeltaBlock);
-  const dim3 grid(n_ent, a.H, (a.V + kDeltaWarps * kDeltaCols - 1) / (kDeltaWarps * kDeltaCols));
-  DLI_LAUNCH("delta_rule", (delta_rule_kernel<E, NS>), grid, dim3(kDeltaWarps * 32), smem, s, qkv, (const E*)proj, St, o, a);
+  const int cpb = delta_cols_per_cta(a.D, NS, CPT);
+  const size_t smem = sizeof(float) * ((size_t)2 * kDeltaBlock * delta_lanes(a.D, NS) * delta_pad(NS) + kDeltaBlock * cpb + 3 * kDeltaBlock);
+  const dim3 grid(n_ent, a.H, (a.V + cpb - 1) / cpb);
+  DLI_LAUNCH("delta_rule", (delta_rule_kernel<E, CPT, NS>), grid, dim3(kDeltaWarps * 32), smem, s, qkv, (const E*)proj, St, o, a);
   return DLI_OK;
 }
 
 template <typename E>
 static int dispatch_delta(const float* qkv, const void* proj, float* St, float* o, int n_ent, const DeltaRun& a,
                           cudaStream_t s) {
-  if (a.D <= 32) return launch_delta<E, 1>(qkv, proj, St, o, n_ent, a, s);
-  if (a.D <= 64) return launch_delta<E, 2>(qkv, proj, St, o, n_ent, a, s);
-  if (a.D <= 128) return launch_delta<E, 4>(qkv, proj, St, o, n_ent, a, s);
-  return launch_delta<E, 8>(qkv, proj, St, o, n_ent, a, s);
+  // two columns per thread (the fewest instructions) where that still gives every SM a few CTAs; else one, and for
+  // few rows of a small key size four state rows per lane, which spreads a decode row's state over 4x as many CTAs
+  auto ctas = [&](int NS, int cpt) {
+    const int cpb = delta_cols_per_cta(a.D, NS, cpt);
+    return (long)n_ent * a.H * ((a.V + cpb - 1) / cpb);
+  };
+  const long sms = sm_count_cached();
+  if (ctas(16, 2) >= 2 * sms) return launch_delta<E, 2, 16>(qkv, proj, St, o, n_ent, a, s);
+  if (ctas(16, 1) >= sms / 2 || a.D > 128 || ctas(4, 1) > 3 * sms) return launch_delta<E, 1, 16>(qkv, proj, St, o, n_ent, a, s);
+  return launch_delta<E, 1, 4>(qkv, proj, St, o, n_ent, a, s);
 }
 
 }  // namespace dli
@@ -213,8 +296,8 @@ int dli_delta_rule_ragged(const float* qkv, const void* proj, float* St, float* 
                           int G, int D, int V, int ldx, int ldp, int b_off, int a_off, const float* a_log,
                           const float* dt_bias, float q_scale, float unit_eps, int dt, dli_stream_t stream) {
   DLI_CHECK_ARG(qkv && proj && St && o && ent && a_log && dt_bias, "dli_delta_rule_ragged: null pointer");
-  DLI_CHECK_ARG(H > 0 && G > 0 && H % G == 0 && D > 0 && D <= 256 && V > 0 && ldx >= 2 * G * D + H * V,
-                "dli_delta_rule_ragged: H=%d G=%d D=%d V=%d ldx=%d (H %% G == 0, D <= 256)", H, G, D, V, ldx);
+  DLI_CHECK_ARG(H > 0 && G > 0 && H % G == 0 && D > 0 && D <= 512 && V > 0 && ldx >= 2 * G * D + H * V,
+                "dli_delta_rule_ragged: H=%d G=%d D=%d V=%d ldx=%d (H %% G == 0, D <= 512)", H, G, D, V, ldx);
   DLI_CHECK_ARG((reinterpret_cast<uintptr_t>(ent) & 15u) == 0, "dli_delta_rule_ragged: ent must be 16-byte aligned");
   DLI_CHECK_ARG(dt == 0 || dt == 1, "element type %d: 0 = bf16, 1 = float", dt);
   if (n_ent <= 0) return DLI_OK;

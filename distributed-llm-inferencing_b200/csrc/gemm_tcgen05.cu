@@ -183,7 +183,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const float gte = round_bf16(v[j]), up = round_bf16(__uint_as_float(r2[j]));
-              v[j] = round_bf16(silu_f(gte)) * up;
+              v[j] = gated_combine(gte, up, kGated ? reinterpret_cast<const float*>(bias) : nullptr);
             }
           } else {
             if (epilogue & DLI_EPI_BIAS) {
@@ -328,7 +328,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
               for (int e = 0; e < 8; ++e) {
                 if (kGated) {
                   const float gte = round_bf16(acc1[q][e]), up = round_bf16(acc2[q][e]);
-                  o[e] = round_bf16(silu_f(gte)) * up;
+                  o[e] = gated_combine(gte, up, kGated ? reinterpret_cast<const float*>(bias) : nullptr);
                 } else {
                   float vv = round_bf16(acc1[q][e] + bvv[e]);
                   if (epilogue & DLI_EPI_GELU_NEW) vv = round_bf16(gelu_new_f(vv));
@@ -370,7 +370,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                 float v;
                 if (kGated) {
                   const float gte = round_bf16(a1[j]), up = round_bf16(a2[j]);
-                  v = round_bf16(silu_f(gte)) * up;
+                  v = gated_combine(gte, up, kGated ? reinterpret_cast<const float*>(bias) : nullptr);
                 } else {
                   v = round_bf16(a1[j] + bv);
                   if (epilogue & DLI_EPI_GELU_NEW) v = round_bf16(gelu_new_f(v));
@@ -667,7 +667,7 @@ gemm_prefill_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const float gte = round_bf16(v[j]), up = round_bf16(__uint_as_float(r2[j]));
-              v[j] = round_bf16(silu_f(gte)) * up;
+              v[j] = gated_combine(gte, up, kGated ? reinterpret_cast<const float*>(bias) : nullptr);
             }
           } else {
             if (epilogue & DLI_EPI_BIAS) {
@@ -873,7 +873,14 @@ int dli_gemm_qkv_rope_append_bf16(const void* x, const void* w_qkv, void* qkv, i
                                                   static_cast<cudaStream_t>(stream), ra);
 }
 
+static int gemm_gated_act(const void* x, const void* w_gu, void* y, int M, int F, int K, const float* act, dli_stream_t stream);
+
 int dli_gemm_gated_silu_bf16(const void* x, const void* w_gu, void* y, int M, int F, int K, dli_stream_t stream) {
+  return gemm_gated_act(x, w_gu, y, M, F, K, nullptr, stream);
+}
+
+// act: NULL or {limit, alpha} on the device (gated_combine); it travels in the bias slot, which gated tiles do not use
+static int gemm_gated_act(const void* x, const void* w_gu, void* y, int M, int F, int K, const float* act, dli_stream_t stream) {
   using namespace dli;
   DLI_CHECK_ARG(x && w_gu && y, "dli_gemm_gated_silu_bf16: null pointer");
   DLI_CHECK_ARG(M >= 0 && F > 0 && F % 128 == 0 && K > 0 && K % 64 == 0,
@@ -883,13 +890,13 @@ int dli_gemm_gated_silu_bf16(const void* x, const void* w_gu, void* y, int M, in
   if (M == 0) return DLI_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int N2 = 2 * F;  // rows of w_gu
-  if (M <= 16) return launch_gemm<16, true, true>(x, w_gu, nullptr, nullptr, y, M, N2, K, 0, s);
-  if (M <= 32) return launch_gemm<32, true, true>(x, w_gu, nullptr, nullptr, y, M, N2, K, 0, s);
-  if (M <= 64) return launch_gemm<64, true, true>(x, w_gu, nullptr, nullptr, y, M, N2, K, 0, s);
-  if (M <= 128) return launch_gemm<128, true, true>(x, w_gu, nullptr, nullptr, y, M, N2, K, 0, s);
+  if (M <= 16) return launch_gemm<16, true, true>(x, w_gu, act, nullptr, y, M, N2, K, 0, s);
+  if (M <= 32) return launch_gemm<32, true, true>(x, w_gu, act, nullptr, y, M, N2, K, 0, s);
+  if (M <= 64) return launch_gemm<64, true, true>(x, w_gu, act, nullptr, y, M, N2, K, 0, s);
+  if (M <= 128) return launch_gemm<128, true, true>(x, w_gu, act, nullptr, y, M, N2, K, 0, s);
   // (256-row tiles measured slower here: 420 against 332 us at 2 048 rows — the gated epilogue is long and would
   // not be overlapped, and 896 tiles make 7 rounds where 1 792 make 13 half as long)
-  return launch_gemm<256, false, true>(x, w_gu, nullptr, nullptr, y, M, N2, K, 0, s);
+  return launch_gemm<256, false, true>(x, w_gu, act, nullptr, y, M, N2, K, 0, s);
 }
 
 size_t dli_gemm_splitk_scratch_bytes(int M, int N) {
@@ -920,10 +927,18 @@ int dli_gemm_splitk_bf16(const void* x, const void* w, const void* bias, const v
   return launch_gemm<128, true, false>(x, w, bias, residual, y, M, N, K, epilogue, s, scratch, scratch_bytes);
 }
 
+static int gemm_splitk_gated_act(const void* x, const void* w_gu, void* y, int M, int F, int K, const float* act, void* scratch,
+                                 size_t scratch_bytes, dli_stream_t stream);
+
 int dli_gemm_splitk_gated_silu_bf16(const void* x, const void* w_gu, void* y, int M, int F, int K, void* scratch,
                                     size_t scratch_bytes, dli_stream_t stream) {
+  return gemm_splitk_gated_act(x, w_gu, y, M, F, K, nullptr, scratch, scratch_bytes, stream);
+}
+
+static int gemm_splitk_gated_act(const void* x, const void* w_gu, void* y, int M, int F, int K, const float* act, void* scratch,
+                                 size_t scratch_bytes, dli_stream_t stream) {
   using namespace dli;
-  if (M > 128 || scratch == nullptr) return dli_gemm_gated_silu_bf16(x, w_gu, y, M, F, K, stream);
+  if (M > 128 || scratch == nullptr) return gemm_gated_act(x, w_gu, y, M, F, K, act, stream);
   DLI_CHECK_ARG(x && w_gu && y, "dli_gemm_splitk_gated_silu_bf16: null pointer");
   DLI_CHECK_ARG(M >= 0 && F > 0 && F % 128 == 0 && K > 0 && K % 64 == 0,
                 "dli_gemm_splitk_gated_silu_bf16: need F %% 128 == 0, K %% 64 == 0 (got M=%d F=%d K=%d)", M, F, K);
@@ -932,10 +947,10 @@ int dli_gemm_splitk_gated_silu_bf16(const void* x, const void* w_gu, void* y, in
   if (M == 0) return DLI_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int N2 = 2 * F;
-  if (M <= 16) return launch_gemm<16, true, true>(x, w_gu, nullptr, nullptr, y, M, N2, K, 0, s, scratch, scratch_bytes);
-  if (M <= 32) return launch_gemm<32, true, true>(x, w_gu, nullptr, nullptr, y, M, N2, K, 0, s, scratch, scratch_bytes);
-  if (M <= 64) return launch_gemm<64, true, true>(x, w_gu, nullptr, nullptr, y, M, N2, K, 0, s, scratch, scratch_bytes);
-  return launch_gemm<128, true, true>(x, w_gu, nullptr, nullptr, y, M, N2, K, 0, s, scratch, scratch_bytes);
+  if (M <= 16) return launch_gemm<16, true, true>(x, w_gu, act, nullptr, y, M, N2, K, 0, s, scratch, scratch_bytes);
+  if (M <= 32) return launch_gemm<32, true, true>(x, w_gu, act, nullptr, y, M, N2, K, 0, s, scratch, scratch_bytes);
+  if (M <= 64) return launch_gemm<64, true, true>(x, w_gu, act, nullptr, y, M, N2, K, 0, s, scratch, scratch_bytes);
+  return launch_gemm<128, true, true>(x, w_gu, act, nullptr, y, M, N2, K, 0, s, scratch, scratch_bytes);
 }
 
 int dli_linear_bf16(const void* x, const void* w, const void* bias, const void* residual, void* y, int M, int N,
@@ -953,6 +968,14 @@ int dli_linear_bf16(const void* x, const void* w, const void* bias, const void* 
 int dli_linear_gated_silu_bf16(const void* x, const void* w_gu, void* y, int M, int F, int K, dli_stream_t stream) {
   if (M <= 2 || K % 64 != 0) return dli_gemv_gated_silu_bf16(x, w_gu, y, M, F, K, stream);
   return dli_gemm_gated_silu_bf16(x, w_gu, y, M, F, K, stream);
+}
+
+int dli_linear_gated_act_bf16(const void* x, const void* w_gu, void* y, int M, int F, int K, const float* act, void* scratch,
+                              size_t scratch_bytes, dli_stream_t stream) {
+  DLI_CHECK_ARG(act, "dli_linear_gated_act_bf16: the activation's parameters are missing");
+  if (M <= 2 || K % 64 != 0) return dli_gemv_gated_act_bf16(x, w_gu, y, M, F, K, act, stream);
+  if (M <= 128 && scratch) return gemm_splitk_gated_act(x, w_gu, y, M, F, K, act, scratch, scratch_bytes, stream);
+  return gemm_gated_act(x, w_gu, y, M, F, K, act, stream);
 }
 
 }  // extern "C"

@@ -246,7 +246,7 @@ gemv_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, const bf16* 
         float v;
         if (kGated) {
           const float g = round_bf16(s), u = round_bf16(s2);
-          v = round_bf16(silu_f(g)) * u;
+          v = gated_combine(g, u, reinterpret_cast<const float*>(bias));
         } else {
           if (epilogue & DLI_EPI_BIAS) s += __bfloat162float(bias[n]);
           v = round_bf16(s);
@@ -383,6 +383,17 @@ int dli_gemv_gated_silu_bf16(const void* x, const void* w_gu, void* y, int M, in
   DLI_CHECK_ARG(F % 128 == 0, "dli_gemv_gated_silu_bf16: need F %% 128 == 0 (got F=%d)", F);
   if (M == 0) return DLI_OK;
   return gemv_dispatch<true, false>(x, w_gu, nullptr, nullptr, y, M, F, K, 0, nullptr, 0.f, stream);
+}
+
+int dli_gemv_gated_act_bf16(const void* x, const void* w_gu, void* y, int M, int F, int K, const float* act,
+                            dli_stream_t stream) {
+  using namespace dli;
+  int rc = check_gemv("dli_gemv_gated_act_bf16", x, w_gu, y, M, F, K);
+  if (rc != DLI_OK) return rc;
+  DLI_CHECK_ARG(F % 128 == 0 && act, "dli_gemv_gated_act_bf16: need F %% 128 == 0 (got F=%d) and the activation's parameters", F);
+  if (M == 0) return DLI_OK;
+  // the parameters travel in the bias slot, which gated tasks do not use
+  return gemv_dispatch<true, false>(x, w_gu, act, nullptr, y, M, F, K, 0, nullptr, 0.f, stream);
 }
 
 int dli_rmsnorm_gemv_bf16(const void* h, const void* ln_w, float eps, const void* w, const void* bias,

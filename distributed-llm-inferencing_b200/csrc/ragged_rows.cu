@@ -35,7 +35,7 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 template <typename E>
 __global__ void __launch_bounds__(1024)
 embedding_f32_kernel(const int32_t* __restrict__ ids, const E* __restrict__ table, float* __restrict__ x,
-                     float* __restrict__ x2, int d, int vocab, float scale) {
+                     float* __restrict__ x2, E* __restrict__ xe, int d, int vocab, float scale) {
   pdl_wait();
   pdl_trigger();
   const size_t row = blockIdx.x;
@@ -45,6 +45,7 @@ embedding_f32_kernel(const int32_t* __restrict__ ids, const E* __restrict__ tabl
     const float v = to_f(table[(size_t)id * d + c]) * scale;
     x[row * d + c] = v;
     if (x2) x2[row * d + c] = v;
+    if (xe) xe[row * d + c] = from_f<E>(v);
   }
 }
 
@@ -489,6 +490,29 @@ token_side_kernel(float* __restrict__ x, const int32_t* __restrict__ ids, const 
     if (he) he[o + k] = from_f<E>(v);
   }
 }
+
+// Per-layer token input for few rows, first half as ONE kernel: g[row, c] = gelu_tanh(w_gate[c] . x[row]) *
+// table[ids[row], off + c], read from the fp32 residual row itself.  Grid (rows, ceil(n / 8)): a warp per gate channel.
+template <typename E>
+__global__ void __launch_bounds__(256)
+token_side_gate_kernel(const float* __restrict__ x, const int32_t* __restrict__ ids, const E* __restrict__ table,
+                       const E* __restrict__ wg, E* __restrict__ g, int d, int n, int ld_tab, int off, int vocab) {
+  pdl_wait();
+  pdl_trigger();
+  const size_t row = blockIdx.x;
+  const int lane = threadIdx.x & 31, c = blockIdx.y * 8 + (threadIdx.x >> 5);
+  if (c >= n) return;
+  const float* xr = x + row * d;
+  const E* wr = wg + (size_t)c * d;
+  float acc = 0.f;
+  for (int k = lane; k < d; k += 32) acc = fmaf(to_f(wr[k]), xr[k], acc);
+  acc = warp_sum(acc);
+  if (lane == 0) {
+    int id = ids[row];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    g[row * n + c] = from_f<E>(gelu_new_f(acc) * to_f(table[(size_t)id * ld_tab + off + c]));
+  }
+}
 }  // namespace dli
 
 using namespace dli;
@@ -500,14 +524,14 @@ static inline int row_threads(int rows, int d) { return (rows <= 64 && d >= 2048
 
 extern "C" {
 
-int dli_embedding_f32(const int32_t* ids, const void* table, float* x, float* x2, int rows, int d, int vocab, float scale,
-                      int dt, dli_stream_t stream) {
+int dli_embedding_f32(const int32_t* ids, const void* table, float* x, float* x2, void* xe, int rows, int d, int vocab,
+                      float scale, int dt, dli_stream_t stream) {
   DLI_CHECK_ARG(ids && table && x && d > 0 && vocab > 0, "dli_embedding_f32: null pointer or empty shape");
   DT_CHECK(dt);
   if (rows <= 0) return DLI_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dt == 0) DLI_LAUNCH("embedding_f32", embedding_f32_kernel<bf16>, dim3(rows), dim3(row_threads(rows, d)), 0, s, ids, (const bf16*)table, x, x2, d, vocab, scale);
-  else DLI_LAUNCH("embedding_f32", embedding_f32_kernel<float>, dim3(rows), dim3(row_threads(rows, d)), 0, s, ids, (const float*)table, x, x2, d, vocab, scale);
+  if (dt == 0) DLI_LAUNCH("embedding_f32", embedding_f32_kernel<bf16>, dim3(rows), dim3(row_threads(rows, d)), 0, s, ids, (const bf16*)table, x, x2, (bf16*)xe, d, vocab, scale);
+  else DLI_LAUNCH("embedding_f32", embedding_f32_kernel<float>, dim3(rows), dim3(row_threads(rows, d)), 0, s, ids, (const float*)table, x, x2, (float*)xe, d, vocab, scale);
   return DLI_OK;
 }
 
@@ -690,6 +714,20 @@ int dli_token_side(float* x, const int32_t* ids, const void* table, const void* 
   const int th = d >= 2048 ? 1024 : (d >= 512 ? 512 : 256);
   if (dt == 0) DLI_LAUNCH("token_side", token_side_kernel<bf16>, dim3(rows), dim3(th), smem, s, x, ids, (const bf16*)table, (const bf16*)w_gate, (const bf16*)w_proj, w, (bf16*)he, d, n, ld_tab, off, vocab, eps);
   else DLI_LAUNCH("token_side", token_side_kernel<float>, dim3(rows), dim3(th), smem, s, x, ids, (const float*)table, (const float*)w_gate, (const float*)w_proj, w, (float*)he, d, n, ld_tab, off, vocab, eps);
+  return DLI_OK;
+}
+
+
+int dli_token_side_gate(const float* x, const int32_t* ids, const void* table, const void* w_gate, void* g, int rows, int d,
+                        int n, int ld_tab, int off, int vocab, int dt, dli_stream_t stream) {
+  DLI_CHECK_ARG(x && ids && table && w_gate && g && d > 0 && n > 0 && off >= 0 && off + n <= ld_tab && vocab > 0,
+                "dli_token_side_gate: null pointer or bad shape");
+  DT_CHECK(dt);
+  if (rows <= 0) return DLI_OK;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const dim3 grid(rows, (n + 7) / 8);
+  if (dt == 0) DLI_LAUNCH("token_side_gate", token_side_gate_kernel<bf16>, grid, dim3(256), 0, s, x, ids, (const bf16*)table, (const bf16*)w_gate, (bf16*)g, d, n, ld_tab, off, vocab);
+  else DLI_LAUNCH("token_side_gate", token_side_gate_kernel<float>, grid, dim3(256), 0, s, x, ids, (const float*)table, (const float*)w_gate, (float*)g, d, n, ld_tab, off, vocab);
   return DLI_OK;
 }
 

@@ -230,6 +230,21 @@ def gemm_gated_silu(x, w_gu, out=None):
     return _gated("dli_gemm_gated_silu_bf16", x, w_gu, out)
 
 
+def linear_gated_act(x, w_gu, act, scratch=None, out=None):
+    """min(g, l) * sigmoid(a min(g, l)) * (clamp(u, -l, l) + 1) with g = x @ Wg.T, u = x @ Wu.T as the projection's epilogue;
+    w_gu = pack_gate_up(Wg, Wu), act float32 [2] = (l, a) on the device; scratch: the split-K buffer (3..128 rows)."""
+    global launch_count
+    _req(x), _req(w_gu), _req(out), _req(act, torch.float32)
+    M, K = x.shape
+    F = w_gu.shape[0] // 2
+    if out is None:
+        out = torch.empty(M, F, dtype=torch.bfloat16, device=x.device)
+    _lib.check("dli_linear_gated_act_bf16", _lib.load().dli_linear_gated_act_bf16(
+        _p(x), _p(w_gu), _p(out), M, F, K, _p(act), _p(scratch), _bytes(scratch), _stream()))
+    launch_count += (M + 3) // 4 if (M <= 2 or K % 64) else 1
+    return out
+
+
 def pack_gate_up(w_gate, w_up):
     """Interleave gate and up rows in blocks of 128 (layout dli.h documents)."""
     F, K = w_gate.shape
@@ -467,11 +482,12 @@ def _i32(*ts):
         _req(t, torch.int32)
 
 
-def embedding_f32(ids, table, out, scale: float = 1.0, out2=None):
-    """ids int32 [rows]; table [V, d] bf16 / float -> out float32 [rows, d] = table[ids] * scale (out2: a second copy)."""
-    _i32(ids), _req(table, table.dtype), _f32(out, out2)
-    _call("dli_embedding_f32", 1, _p(ids), _p(table), _p(out), _p(out2), ids.numel(), table.shape[1], table.shape[0],
-          float(scale), _dt(table), _stream())
+def embedding_f32(ids, table, out, scale: float = 1.0, out2=None, out_e=None):
+    """ids int32 [rows]; table [V, d] bf16 / float -> out float32 [rows, d] = table[ids] * scale (out2: a second copy;
+    out_e: a copy in the table's element type)."""
+    _i32(ids), _req(table, table.dtype), _f32(out, out2), _req(out_e, table.dtype)
+    _call("dli_embedding_f32", 1, _p(ids), _p(table), _p(out), _p(out2), _p(out_e), ids.numel(), table.shape[1],
+          table.shape[0], float(scale), _dt(table), _stream())
     return out
 
 
@@ -782,6 +798,14 @@ def token_side_act(s, ids, table, off: int, out):
     _req(s, s.dtype), _req(table, s.dtype), _req(out, s.dtype), _i32(ids)
     _call("dli_token_side_act", 1, _p(s), _p(ids), _p(table), _p(out), s.shape[0], s.shape[1], table.shape[1], int(off),
           table.shape[0], _dt(s), _stream())
+    return out
+
+
+def token_side_gate(x, ids, table, off: int, w_gate, out):
+    """Few rows: out [rows, n] = gelu_tanh(x @ w_gate.T) * table[ids, off : off + n] in one kernel (x float32)."""
+    _f32(x), _i32(ids), _req(table, table.dtype), _req(w_gate, table.dtype), _req(out, table.dtype)
+    _call("dli_token_side_gate", 1, _p(x), _p(ids), _p(table), _p(w_gate), _p(out), x.shape[0], x.shape[1], w_gate.shape[0],
+          table.shape[1], int(off), table.shape[0], _dt(table), _stream())
     return out
 
 

@@ -212,7 +212,8 @@ class RaggedEngine:
         self.moe_sel_max_rows = 8                  # up to this many rows a step reads only the chosen experts' weights ...
         self.moe_sel_share = 3.0                   # ... if they are at most 1/3 of all expert weights: the dense weight stream runs
                                                    # at ~0.63 of the HBM peak, the gathered one at ~0.2 (measured, 2048-wide)
-        self.side_fused_max_rows = 16              # up to this many rows the per-layer token input is one kernel
+        self.side_fused_max_rows = 16              # up to this many rows the per-layer token input is one kernel ...
+        self.side_fused_max_bytes = 64 << 10       # ... if its two matrices are at most this large (else: weight streams)
         self.latent_expand_max_elems = 1 << 31     # scratch bound (4 GiB in bf16) of the per-head expansion of cached latents
         self.mlstm_parallel_max_floats = 1 << 28   # scratch bound (1 GiB) of the block-parallel mLSTM / state-space scan; beyond it: blocks in order
         self.layer_trace: Optional[list] = None    # set to [] to collect the residual stream after every layer
@@ -324,7 +325,14 @@ class RaggedEngine:
                 d["side_norm"] = vec(src["side_norm"])
             if L.ff and L.post_only:
                 d["norm2"] = vec(src["norm2"])
-                d["w_gu"] = mat(src["gate"], src["up"])  # [gate rows | up rows]: the clamped activation is its own kernel
+                # the tensor-core path interleaves gate and up rows so that the clamped activation is the GEMM's epilogue;
+                # other shapes: [gate rows | up rows] and the activation as a kernel of its own
+                d["packed"] = E == BF and L.ff % 128 == 0 and s.width % 8 == 0
+                if d["packed"]:
+                    d["w_gu"] = ops.pack_gate_up(src["gate"].to(BF), src["up"].to(BF)).to(dev)
+                    d["ff_act"] = torch.tensor([L.ff_limit, L.ff_alpha], dtype=torch.float32, device=dev)
+                else:
+                    d["w_gu"] = mat(src["gate"], src["up"])
                 d["w_down"] = mat(src["down"], pad_rows=False)
             elif L.ff:
                 d["norm2"], d["norm2b"] = float(src["norm2"]), float(src["norm2b"])
@@ -594,7 +602,9 @@ class RaggedEngine:
             ops.causal_conv_ragged(hn, tail, taps_w, d_rent, d_ent, hc)  # one tap: no tail, h * (1 + w)
 
         x0 = self._x0[:rows] if s.loop_passes else None
-        ops.embedding_f32(d_tok, self.w["embed"], x, s.embed_scale, out2=x0)
+        # a first layer that reads the residual stream itself gets its GEMM operand from the same kernel
+        first_post = s.layers and s.layers[0].post_only and E != torch.float32
+        ops.embedding_f32(d_tok, self.w["embed"], x, s.embed_scale, out2=x0, out_e=hc if first_post else None)
         pt = self.kv.page_table
         y_prev, g_prev = None, 1.0
         for li, L in enumerate(s.layers):
@@ -704,7 +714,7 @@ class RaggedEngine:
         d_tok, d_rent, d_ent, d_want, d_tiles = views
         x, y = self._x[:rows], self._y[:rows]
         he = None if E == torch.float32 else self._hc[:rows]
-        prev_same = li > 0 and s.layers[li - 1].post_only
+        prev_same = s.layers[li - 1].post_only if li > 0 else s.layers[0].reenter is None
         h = self._operand(rows, refresh=not prev_same)
         m = L.mixer
         n_proj = P["w_proj"].shape[0]
@@ -724,23 +734,32 @@ class RaggedEngine:
         self._lin(mix, P["wo"], y)
         ops.postnorm_vec_add(y, x, P["norm1"], s.eps, he=he)
         if L.ff:
-            n_gu = P["w_gu"].shape[0]
-            gu = self._gu[:rows * n_gu].view(rows, n_gu)
-            self._lin(h, P["w_gu"], gu)
             act = self._act[:rows * L.ff].view(rows, L.ff)
-            ops.moe_act(gu, None, act, 0, 0, 0.0, ff_s=L.ff, limit_s=L.ff_limit, alpha=L.ff_alpha)
+            if P["packed"]:
+                ops.linear_gated_act(h, P["w_gu"], P["ff_act"], self._splitk() if 2 < rows <= 128 and s.width % 64 == 0 else None,
+                                     out=act)
+            else:
+                n_gu = P["w_gu"].shape[0]
+                gu = self._gu[:rows * n_gu].view(rows, n_gu)
+                self._lin(h, P["w_gu"], gu)
+                ops.moe_act(gu, None, act, 0, 0, 0.0, ff_s=L.ff, limit_s=L.ff_limit, alpha=L.ff_alpha)
             self._lin(act, P["w_down"], y)
             ops.postnorm_vec_add(y, x, P["norm2"], s.eps, he=he)
         if L.side_dim:
             n = L.side_dim
-            if rows <= self.side_fused_max_rows and (2 * s.width + n) * 4 <= 48 * 1024:
+            # the one-kernel form reads both matrices with ONE CTA per row: only where they are small enough for that
+            if rows <= self.side_fused_max_rows and (2 * s.width + n) * 4 <= 48 * 1024 and \
+                    2 * s.width * n * P["side_gate"].element_size() <= self.side_fused_max_bytes:
                 ops.token_side(x, d_tok, self.w["side_embed"], L.side_off, P["side_gate"], P["side_proj"], P["side_norm"],
                                s.eps, he=he)
             else:
-                sg = self._sg[:rows * n].view(rows, n)
                 sa = self._sa[:rows * n].view(rows, n)
-                self._lin(h, P["side_gate"], sg)
-                ops.token_side_act(sg, d_tok, self.w["side_embed"], L.side_off, sa)
+                if rows <= self.side_fused_max_rows:
+                    ops.token_side_gate(x, d_tok, self.w["side_embed"], L.side_off, P["side_gate"], sa)
+                else:
+                    sg = self._sg[:rows * n].view(rows, n)
+                    self._lin(h, P["side_gate"], sg)
+                    ops.token_side_act(sg, d_tok, self.w["side_embed"], L.side_off, sa)
                 self._lin(sa, P["side_proj"], y)
                 ops.postnorm_vec_add(y, x, P["side_norm"], s.eps, he=he)
 

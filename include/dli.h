@@ -262,6 +262,15 @@ int dli_gemm_gated_silu_bf16(const void* x, const void* w_gu, void* y, int M, in
                              int K, dli_stream_t stream);
 int dli_linear_gated_silu_bf16(const void* x, const void* w_gu, void* y, int M,
                                int F, int K, dli_stream_t stream);
+/* The same gated projection pair with the clamped activation g * sigmoid(alpha g) * (u + 1), g = min(gate, limit),
+ * u = clamp(up, -limit, limit), in the epilogue; act points at {limit, alpha} (two floats) on the device.  w_gu in
+ * the interleaved layout of dli_gemv_gated_silu_bf16.  dli_linear_gated_act_bf16 picks the weight stream (M <= 2 or
+ * K % 64 != 0), the split-K tensor-core stream (M <= 128 with scratch of dli_gemm_splitk_scratch_bytes) or the
+ * tensor-core GEMM. */
+int dli_gemv_gated_act_bf16(const void* x, const void* w_gu, void* y, int M, int F, int K, const float* act,
+                            dli_stream_t stream);
+int dli_linear_gated_act_bf16(const void* x, const void* w_gu, void* y, int M, int F, int K, const float* act, void* scratch,
+                              size_t scratch_bytes, dli_stream_t stream);
 
 /* The qkv projection of a PROMPT pass fused with RoPE and the KV-cache append:
  *   qkv = x @ w_qkv^T  (rounded to bf16), then exactly what dli_rope_kv_append_bf16
@@ -401,9 +410,10 @@ int dli_decode_advance(const int32_t* tokens, int32_t* token_log, int32_t* posit
  * caches: 0 = bf16, 1 = float (true fp32 arithmetic).  The residual stream x,
  * every norm, convolution state, recurrent state, angle, score and softmax weight
  * is fp32 for both. */
-/* x = table[ids] * scale as fp32; x2 (optional) receives the same rows (a model that re-reads its embedding output). */
-int dli_embedding_f32(const int32_t* ids, const void* table, float* x, float* x2, int rows, int d, int vocab, float scale,
-                      int dt, dli_stream_t stream);
+/* x = table[ids] * scale as fp32; x2 (optional) receives the same rows (a model that re-reads its embedding output),
+ * xe (optional) the same rows in the element type (a first layer that reads the residual stream as a GEMM operand). */
+int dli_embedding_f32(const int32_t* ids, const void* table, float* x, float* x2, void* xe, int rows, int d, int vocab,
+                      float scale, int dt, dli_stream_t stream);
 /* RMS norm in `groups` equal consecutive parts of the row, each by its own root mean square, times w [d] fp32;
  * hn (fp32) and he (element type dt) are optional outputs. */
 int dli_group_rmsnorm(const float* x, const float* w, float* hn, void* he, int rows, int d, int groups, float eps, int dt,
@@ -564,12 +574,15 @@ int dli_moe_sel_bf16(const void* x, const void* w_gu, const void* w_down, const 
  * element type) = x afterwards, the next sublayer's GEMM operand.
  * Per-layer token input: table [vocab, ld_tab] holds every layer's n-wide part of a token's side embedding at column
  * off; dli_token_side_act: g [rows, n] = gelu_tanh(s) * table[ids[row], off : off + n] (s = the gate projection of x);
+ * dli_token_side_gate: the same g for few rows straight from the fp32 rows x (gate projection included);
  * dli_token_side does the whole update for few rows in one kernel: y = w_proj (gelu_tanh(w_gate x) * table[..]),
  * x += y / sqrt(mean(y^2) + eps) * w, he = x. */
 int dli_postnorm_vec_add(const void* y, float* x, const float* w, void* he, int rows, int d, float eps, int dt,
                          dli_stream_t stream);
 int dli_token_side_act(const void* s, const int32_t* ids, const void* table, void* g, int rows, int n, int ld_tab, int off,
                        int vocab, int dt, dli_stream_t stream);
+int dli_token_side_gate(const float* x, const int32_t* ids, const void* table, const void* w_gate, void* g, int rows, int d,
+                        int n, int ld_tab, int off, int vocab, int dt, dli_stream_t stream);
 int dli_token_side(float* x, const int32_t* ids, const void* table, const void* w_gate, const void* w_proj, const float* w,
                    void* he, int rows, int d, int n, int ld_tab, int off, int vocab, float eps, int dt, dli_stream_t stream);
 

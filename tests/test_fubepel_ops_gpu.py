@@ -254,3 +254,21 @@ def test_tensor_core_tiles_with_kept_first_positions(cuts):
         for h in range(2):
             want = R.softmax_attend((R.rms_norm(u[:, 64 * h:64 * h + 64], None, 1e-5) @ kn.T) * 0.4, u[:, 192:], vis)
             assert (got[:, h] - want).abs().max() < 0.06, (size, keep, h)
+
+
+@pytest.mark.parametrize("rows", [1, 2, 5, 40, 200])
+def test_clamped_activation_as_the_projection_epilogue(rows):
+    """bfloat16 weights with ff a multiple of 128: the gate/up projection carries the clamped activation in its
+    epilogue on every path (weight stream, split-K stream, tensor-core GEMM); against the oracle on the same weights."""
+    from dli_b200 import ops
+
+    torch.manual_seed(rows)
+    W, ff, limit = 128, 256, 1.1
+    x = (torch.randn(rows, W) * 1.5).bfloat16()
+    wg, wu = (torch.randn(ff, W) * 0.2).bfloat16(), (torch.randn(ff, W) * 0.2).bfloat16()
+    w_gu = ops.pack_gate_up(wg, wu).to(DEV)
+    act = torch.tensor([limit, 1.702], device=DEV)
+    scratch = torch.zeros(ops.gemm_splitk_scratch_bytes(128, 2 * ff), dtype=torch.uint8, device=DEV)
+    got = ops.linear_gated_act(x.to(DEV), w_gu, act, scratch if 2 < rows <= 128 else None)
+    want = R.clamped_ff(x.double(), {"gate": wg.double(), "up": wu.double(), "down": torch.eye(ff, dtype=F64)}, limit)
+    assert (want.abs() > 1.5).any() and (got.double().cpu() - want).abs().max() < 0.03
