@@ -505,7 +505,18 @@ token_side_gate_kernel(const float* __restrict__ x, const int32_t* __restrict__ 
   const float* xr = x + row * d;
   const E* wr = wg + (size_t)c * d;
   float acc = 0.f;
-  for (int k = lane; k < d; k += 32) acc = fmaf(to_f(wr[k]), xr[k], acc);
+  if (sizeof(E) == 2 && d % 8 == 0 && (reinterpret_cast<uintptr_t>(wr) & 15u) == 0) {
+    // 16 bytes of weights (8 entries) per lane and load
+    for (int k = lane * 8; k < d; k += 256) {
+      float w8[8];
+      unpack8(ld_16B(wr + k), w8);
+      const float4 x0 = *reinterpret_cast<const float4*>(xr + k), x1 = *reinterpret_cast<const float4*>(xr + k + 4);
+      acc = fmaf(w8[0], x0.x, acc); acc = fmaf(w8[1], x0.y, acc); acc = fmaf(w8[2], x0.z, acc); acc = fmaf(w8[3], x0.w, acc);
+      acc = fmaf(w8[4], x1.x, acc); acc = fmaf(w8[5], x1.y, acc); acc = fmaf(w8[6], x1.z, acc); acc = fmaf(w8[7], x1.w, acc);
+    }
+  } else {
+    for (int k = lane; k < d; k += 32) acc = fmaf(to_f(wr[k]), xr[k], acc);
+  }
   acc = warp_sum(acc);
   if (lane == 0) {
     int id = ids[row];

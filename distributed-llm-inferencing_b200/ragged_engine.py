@@ -422,6 +422,10 @@ class RaggedEngine:
             # partial sums of the key splits of decode rows (rows * heads * splits <= 8 * SMs + rows * heads)
             self._apart = torch.empty((8 * self._sms + 16 * max(m.heads for m in lat)) * (max(m.kv_rank for m in lat) + 2),
                                       dtype=f32, device=dev)
+        att = [m for m in mx if m.kind == "attention"]
+        if att:
+            self._apart_att = torch.empty((8 * self._sms + 16 * max(m.heads for m in att)) * (max(m.vdim for m in att) + 2),
+                                          dtype=f32, device=dev)
         ssm = [m for m in mx if m.kind in ("mamba2", "delta")]
         if ssm:
             # fp32 outputs of a recurrent mixer's short convolution (x | B | C, or q | k | v)
@@ -781,9 +785,12 @@ class RaggedEngine:
                                m.scale, chunk=m.chunk, window=m.window, sink=P["sink"], g_off=off["g"],
                                cos_v=cv, sin_v=sv, first=m.keep_first)
         else:
+            # few rows (decode): every row's keys go to several CTAs, so that a long context is read by many SMs; the
+            # count depends on the rows alone (a replayed graph keeps it while the contexts grow)
+            splits = max(1, min(16, (4 * self._sms) // (rows * m.heads))) if rows <= 16 else 1
             ops.attn_ragged(qbuf, kc, vc, proj, mix, d_rent, d_ent, pt, m.heads, m.kv_heads, m.dim, m.vdim,
                             m.scale, chunk=m.chunk, window=m.window, sink=P["sink"], g_off=off["g"], cos_v=cv,
-                            sin_v=sv, first=m.keep_first)
+                            sin_v=sv, first=m.keep_first, splits=splits, part=self._apart_att if splits > 1 else None)
 
     def _delta(self, li, m, P, proj, mix, rows, views):
         """Gated delta rule: short convolutions and SiLU of q | k | v (fp32), the recurrence over the state slot, then
