@@ -116,7 +116,17 @@ latent_q_absorb_kernel(const E* __restrict__ q, const E* __restrict__ uk, float*
     float acc[kLatRows];
 #pragma unroll
     for (int r = 0; r < kLatRows; ++r) acc[r] = 0.f;
-    for (int d = 0; d < D; ++d) {
+    int d = 0;
+    for (; d + 8 <= D; d += 8) {  // eight weight loads in flight before the first is used
+      float wv[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) wv[u] = l_to_f(w[(size_t)(d + u) * K + k]);
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+#pragma unroll
+        for (int r = 0; r < kLatRows; ++r) acc[r] = fmaf(qs[r * D + d + u], wv[u], acc[r]);
+    }
+    for (; d < D; ++d) {
       const float wv = l_to_f(w[(size_t)d * K + k]);
 #pragma unroll
       for (int r = 0; r < kLatRows; ++r) acc[r] = fmaf(qs[r * D + d], wv, acc[r]);
@@ -147,14 +157,19 @@ template <typename E>
 __global__ void __launch_bounds__(256)
 latent_v_up_kernel(const E* __restrict__ o, const E* __restrict__ uv, const E* __restrict__ proj, E* __restrict__ out,
                    int rows, int H, int V, int K, int ldp, int g_off) {
-  extern __shared__ float os[];  // [kLatRows][K]
+  extern __shared__ float os[];  // [kLatRows][Kp], Kp = K rounded up to 256
   pdl_wait();
   pdl_trigger();
   const int r0 = blockIdx.x * kLatRows, h = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int nr = min(kLatRows, rows - r0), nw = blockDim.x >> 5;
+  const int Kp = (K + 255) / 256 * 256;
+  // 16-byte weight loads give lane l entries 8l .. 8l+7 of every 256: entry j of lane l sits at j * 32 + l of its block of
+  // 256, so that the lanes of a warp read consecutive words
+  const bool vec = sizeof(E) == 2 && K % 8 == 0 && (reinterpret_cast<uintptr_t>(uv) & 15u) == 0;
   for (int i = tid; i < kLatRows * K; i += blockDim.x) {
     const int r = i / K, k = i - r * K;
-    os[i] = r < nr ? l_to_f(o[((size_t)(r0 + r) * H + h) * K + k]) : 0.f;
+    const int at = vec ? (k & ~255) + (k & 7) * 32 + ((k & 255) >> 3) : k;
+    os[r * Kp + at] = r < nr ? l_to_f(o[((size_t)(r0 + r) * H + h) * K + k]) : 0.f;
   }
   __syncthreads();
   for (int v = blockIdx.z * nw + warp; v < V; v += nw * gridDim.z) {
@@ -162,10 +177,22 @@ latent_v_up_kernel(const E* __restrict__ o, const E* __restrict__ uv, const E* _
     float acc[kLatRows];
 #pragma unroll
     for (int r = 0; r < kLatRows; ++r) acc[r] = 0.f;
-    for (int k = lane; k < K; k += 32) {
-      const float wv = l_to_f(w[k]);
+    if (vec) {
+      for (int k = lane * 8; k < K; k += 256) {  // 16 bytes of weights per lane and load
+        const uint4 u4 = *reinterpret_cast<const uint4*>(w + k);
+        const float w8[8] = {bf_lo(u4.x), bf_hi(u4.x), bf_lo(u4.y), bf_hi(u4.y), bf_lo(u4.z), bf_hi(u4.z), bf_lo(u4.w), bf_hi(u4.w)};
+        const float* ob = os + (k & ~255) + lane;
 #pragma unroll
-      for (int r = 0; r < kLatRows; ++r) acc[r] = fmaf(os[r * K + k], wv, acc[r]);
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+          for (int r = 0; r < kLatRows; ++r) acc[r] = fmaf(ob[r * Kp + j * 32], w8[j], acc[r]);
+      }
+    } else {
+      for (int k = lane; k < K; k += 32) {
+        const float wv = l_to_f(w[k]);
+#pragma unroll
+        for (int r = 0; r < kLatRows; ++r) acc[r] = fmaf(os[r * Kp + k], wv, acc[r]);
+      }
     }
 #pragma unroll
     for (int r = 0; r < kLatRows; ++r) acc[r] = warp_sum(acc[r]);
@@ -251,8 +278,8 @@ int dli_latent_q_absorb(const void* q, const void* uk, float* qbuf, const int32_
   DLI_CHECK_ARG(dt == 0 || dt == 1, "element type %d: 0 = bf16, 1 = float", dt);
   if (rows <= 0) return DLI_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int th = K >= 256 ? 256 : 128;
-  // few rows (decode): a head's outputs are dealt to several CTAs so that the up-projection is read by many SMs
+  // few rows (decode): a head's outputs are dealt to several CTAs of 64 threads so that the up-projection is read by many SMs
+  const int th = rows <= 16 ? 64 : (K >= 256 ? 256 : 128);
   const dim3 grid((rows + kLatRows - 1) / kLatRows, H, rows <= 16 ? (K + th - 1) / th : 1);
   const size_t smem = (size_t)kLatRows * D * sizeof(float);
   if (dt == 0) DLI_LAUNCH("latent_q_absorb", latent_q_absorb_kernel<bf16>, grid, dim3(th), smem, s, (const bf16*)q, (const bf16*)uk, qbuf, row_ent, ent, cos_t, sin_t, rows, H, D, R, K, halves, ldq ? ldq : H * (D + R));
@@ -263,13 +290,13 @@ int dli_latent_q_absorb(const void* q, const void* uk, float* qbuf, const int32_
 int dli_latent_v_up(const void* o, const void* uv, const void* proj, void* out, int rows, int H, int V, int K, int ldp,
                     int g_off, int dt, dli_stream_t stream) {
   DLI_CHECK_ARG(o && uv && out && (g_off < 0 || proj), "dli_latent_v_up: null pointer");
-  DLI_CHECK_ARG(H > 0 && V > 0 && K > 0 && (size_t)kLatRows * K * sizeof(float) <= 48 * 1024,
+  DLI_CHECK_ARG(H > 0 && V > 0 && K > 0 && (size_t)kLatRows * ((K + 255) / 256 * 256) * sizeof(float) <= 48 * 1024,
                 "dli_latent_v_up: H=%d V=%d K=%d (K <= %d)", H, V, K, 48 * 1024 / (kLatRows * 4));
   DLI_CHECK_ARG(dt == 0 || dt == 1, "element type %d: 0 = bf16, 1 = float", dt);
   if (rows <= 0) return DLI_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const dim3 grid((rows + kLatRows - 1) / kLatRows, H, rows <= 16 ? (V + 31) / 32 : 1);
-  const size_t smem = (size_t)kLatRows * K * sizeof(float);
+  const size_t smem = (size_t)kLatRows * ((K + 255) / 256 * 256) * sizeof(float);
   if (dt == 0) DLI_LAUNCH("latent_v_up", latent_v_up_kernel<bf16>, grid, dim3(256), smem, s, (const bf16*)o, (const bf16*)uv, (const bf16*)proj, (bf16*)out, rows, H, V, K, ldp, g_off);
   else DLI_LAUNCH("latent_v_up", latent_v_up_kernel<float>, grid, dim3(256), smem, s, (const float*)o, (const float*)uv, (const float*)proj, (float*)out, rows, H, V, K, ldp, g_off);
   return DLI_OK;
