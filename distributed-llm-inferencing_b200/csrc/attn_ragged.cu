@@ -378,6 +378,188 @@ attn_ragged_merge_kernel(const E* __restrict__ proj, E* __restrict__ out, AttnRu
   }
 }
 
+// ---- one key/value head shared by all query heads (latent attention over the cached rows, multi-query attention) ----
+// The row-wise kernel above gives every (row, head) its own CTAs, so H heads read the same cached rows H times.  Here a CTA
+// takes HPC heads of a row: a thread loads its key once and forms HPC dot products, and a value load feeds HPC accumulators.
+// Plain causal mask, optional sink, key splits; values in the vector form (4 consecutive dimensions per thread).
+__device__ __forceinline__ void load8(const bf16* p, float* f) { unpack8(ld_16B(p), f); }
+__device__ __forceinline__ void load8(const float* p, float* f) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+
+template <typename E, int HPC>
+__global__ void __launch_bounds__(kAttnThreads)
+attn_shared_kv_kernel(const float* __restrict__ qbuf, const E* __restrict__ kc, const E* __restrict__ vc,
+                      E* __restrict__ out, AttnRun a) {
+  extern __shared__ float sm[];
+  const int groups = attn_value_groups(a.V, a.ldv);
+  float* q = sm;                               // [HPC][D]
+  float* p = q + HPC * a.D;                    // [HPC][128]
+  float* red = p + HPC * kAttnThreads;         // [2][HPC][4]: warp maxima, warp sums
+  float* ov = red + 2 * HPC * 4;               // [groups][HPC][V]
+  pdl_wait();
+  pdl_trigger();
+  const int row = blockIdx.x, h0 = blockIdx.y * HPC, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int4 e = reinterpret_cast<const int4*>(a.ent)[a.row_ent[row]];
+  const int pos = e.w + (row - e.y);
+  const int32_t* pt = a.page_table + (size_t)e.x * a.max_pages;
+  for (int i = tid; i < HPC * a.D; i += kAttnThreads) q[i] = qbuf[((size_t)row * a.H + h0) * a.D + i] * a.scale;
+  int jb = 0, je = pos;
+  if (a.splits > 1) {
+    const int per = (pos + a.splits) / a.splits;
+    jb = (int)blockIdx.z * per;
+    je = min(pos, jb + per - 1);
+  }
+  const int tpg = a.V / 4;                     // threads that cover a value row
+  const int my_group = tid / tpg, d0 = (tid % tpg) * 4;
+  const bool pv_active = my_group < groups;
+  float acc[HPC][4], m[HPC], l[HPC];
+  const bool has_sink = a.sink && blockIdx.z == 0;
+#pragma unroll
+  for (int h = 0; h < HPC; ++h) {
+    acc[h][0] = acc[h][1] = acc[h][2] = acc[h][3] = 0.f;
+    m[h] = has_sink ? a.sink[h0 + h] : -INFINITY;
+    l[h] = has_sink ? 1.f : 0.f;
+  }
+  __syncthreads();
+  for (int j0 = jb; j0 <= je; j0 += kAttnThreads) {
+    const int j = j0 + tid;
+    const bool valid = j <= je;
+    float s[HPC];
+#pragma unroll
+    for (int h = 0; h < HPC; ++h) s[h] = 0.f;
+    if (valid) {
+      const E* kr = kc + ((size_t)pt[j / a.page_size] * a.page_size + j % a.page_size) * a.D;
+      int c = 0;
+      for (; c + 32 <= a.D; c += 32) {  // four 16-byte key loads in flight before the first is used
+        float f[4][8];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) load8(kr + c + 8 * u, f[u]);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+#pragma unroll
+          for (int h = 0; h < HPC; ++h)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) s[h] = fmaf(q[h * a.D + c + 8 * u + i], f[u][i], s[h]);
+      }
+      for (; c < a.D; c += 8) {
+        float f[8];
+        load8(kr + c, f);
+#pragma unroll
+        for (int h = 0; h < HPC; ++h)
+#pragma unroll
+          for (int i = 0; i < 8; ++i) s[h] = fmaf(q[h * a.D + c + i], f[i], s[h]);
+      }
+    }
+#pragma unroll
+    for (int h = 0; h < HPC; ++h) {
+      if (!valid) s[h] = -INFINITY;
+      const float mx = warp_max(s[h]);
+      if (lane == 0) red[h * 4 + warp] = mx;
+    }
+    __syncthreads();
+    float corr[HPC];
+#pragma unroll
+    for (int h = 0; h < HPC; ++h) {
+      const float mx = fmaxf(fmaxf(red[h * 4], red[h * 4 + 1]), fmaxf(red[h * 4 + 2], red[h * 4 + 3]));
+      const float m_new = fmaxf(m[h], mx);
+      corr[h] = (m[h] == -INFINITY) ? 0.f : expf(m[h] - m_new);
+      const float w = valid ? expf(s[h] - m_new) : 0.f;
+      p[h * kAttnThreads + tid] = w;
+      const float ws = warp_sum(w);
+      if (lane == 0) red[HPC * 4 + h * 4 + warp] = ws;
+      m[h] = m_new;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int h = 0; h < HPC; ++h) {
+      const float* r2 = red + HPC * 4 + h * 4;
+      l[h] = l[h] * corr[h] + (r2[0] + r2[1] + r2[2] + r2[3]);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[h][i] *= corr[h];
+    }
+    const int cnt = min(kAttnThreads, je - j0 + 1);
+    if (pv_active) {
+      constexpr int KR = 8;  // keys per round: their page lookups and value loads are in flight together
+      for (int jj = my_group; jj < cnt; jj += KR * groups) {
+        float f[KR][4];
+        int ju[KR];
+#pragma unroll
+        for (int u = 0; u < KR; ++u) {
+          ju[u] = jj + u * groups;
+          const int jk = j0 + min(ju[u], cnt - 1);
+          load4(vc + ((size_t)pt[jk / a.page_size] * a.page_size + jk % a.page_size) * a.ldv + d0, f[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < KR; ++u) {
+          if (ju[u] < cnt) {
+#pragma unroll
+            for (int h = 0; h < HPC; ++h) {
+              const float wj = p[h * kAttnThreads + ju[u]];
+#pragma unroll
+              for (int i = 0; i < 4; ++i) acc[h][i] = fmaf(wj, f[u][i], acc[h][i]);
+            }
+          }
+        }
+      }
+    }
+    __syncthreads();  // p and red are written again by the next pass
+  }
+  if (pv_active) {
+#pragma unroll
+    for (int h = 0; h < HPC; ++h)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) ov[((size_t)my_group * HPC + h) * a.V + d0 + i] = acc[h][i];
+  }
+  __syncthreads();
+  for (int i = tid; i < HPC * a.V; i += kAttnThreads) {
+    const int h = i / a.V, d = i - h * a.V;
+    float u = 0.f;
+    for (int gg = 0; gg < groups; ++gg) u += ov[((size_t)gg * HPC + h) * a.V + d];
+    if (a.splits > 1) a.part[(((size_t)row * a.H + h0 + h) * a.splits + blockIdx.z) * (a.V + 2) + d] = u;
+    else {
+      // l of head h: every thread holds all HPC values; pick by index without dynamic register indexing
+      float lh = l[0];
+#pragma unroll
+      for (int x = 1; x < HPC; ++x) if (h == x) lh = l[x];
+      out[((size_t)row * a.H + h0 + h) * a.V + d] = a_from_f<E>(u / lh);
+    }
+  }
+  if (a.splits > 1 && tid < HPC) {
+    float mh = m[0], lh = l[0];
+#pragma unroll
+    for (int x = 1; x < HPC; ++x) if (tid == x) { mh = m[x]; lh = l[x]; }
+    float* pr = a.part + (((size_t)row * a.H + h0 + tid) * a.splits + blockIdx.z) * (a.V + 2);
+    pr[a.V] = mh;
+    pr[a.V + 1] = lh;
+  }
+}
+
+template <typename E, int HPC>
+static int launch_shared_kv(const float* qbuf, const void* kc, const void* vc, void* out, int rows, const AttnRun& a,
+                            cudaStream_t s) {
+  const int groups = attn_value_groups(a.V, a.ldv);
+  const size_t smem = sizeof(float) * ((size_t)HPC * a.D + HPC * kAttnThreads + 2 * HPC * 4 + (size_t)groups * HPC * a.V);
+  DLI_LAUNCH("attn_shared_kv", (attn_shared_kv_kernel<E, HPC>), dim3(rows, a.H / HPC, a.splits), dim3(kAttnThreads), smem, s, qbuf,
+             (const E*)kc, (const E*)vc, (E*)out, a);
+  return DLI_OK;
+}
+
+// Does a step of this shape take the shared-key/value kernel, and with how many heads per CTA (0: no)?
+static int shared_kv_heads(int H, int G, int D, int V, int ldv, int chunk, int window, int g_off, const float* cos_v, int dt,
+                           const void* kc, const void* vc) {
+  if (G != 1 || H < 2 || chunk > 0 || window > 0 || g_off >= 0 || cos_v) return 0;
+  const size_t es = dt == 0 ? 2 : 4;
+  if (D % 8 != 0 || !attn_vec_values(V, ldv) || (ldv * es) % (dt == 0 ? 8 : 16) != 0 || !aligned16(kc) ||
+      (reinterpret_cast<uintptr_t>(vc) & 15u) != 0)
+    return 0;
+  const int hpc = H % 4 == 0 ? 4 : (H % 2 == 0 ? 2 : 0);
+  if (!hpc) return 0;
+  const size_t smem = sizeof(float) * ((size_t)hpc * D + hpc * kAttnThreads + 2 * hpc * 4 + (size_t)attn_value_groups(V, ldv) * hpc * V);
+  return smem <= 48 * 1024 ? hpc : 0;
+}
+
 // ---- portions of prompts: the same attention on the tensor cores (bf16 caches) ---------------------------------
 // One CTA per (64-row query tile of one entry, query head); 4 warps x 16 rows; key/value tiles of 64 positions
 // (aligned to multiples of 64 in the sequence) staged from the pages with 16-byte cp.async, double-buffered and
@@ -641,6 +823,15 @@ int dli_attn_ragged(const float* qbuf, const void* k_cache, const void* v_cache,
   const size_t smem = sizeof(float) * (D + kAttnThreads + 8 + (size_t)groups * V);
   DLI_CHECK_ARG(smem <= 48 * 1024, "dli_attn_ragged: key size %d needs %zu bytes of shared memory", D, smem);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int hpc = shared_kv_heads(H, G, D, V, ldv ? ldv : V, chunk, window, g_off, cos_v, dt, k_cache, v_cache);
+  if (hpc) {
+    int rc;
+    if (dt == 0) rc = hpc == 4 ? launch_shared_kv<bf16, 4>(qbuf, k_cache, v_cache, out, rows, a, s)
+                               : launch_shared_kv<bf16, 2>(qbuf, k_cache, v_cache, out, rows, a, s);
+    else rc = hpc == 4 ? launch_shared_kv<float, 4>(qbuf, k_cache, v_cache, out, rows, a, s)
+                       : launch_shared_kv<float, 2>(qbuf, k_cache, v_cache, out, rows, a, s);
+    if (rc != DLI_OK) return rc;
+  } else
   if (dt == 0) DLI_LAUNCH("attn_ragged", attn_ragged_kernel<bf16>, dim3(rows, H, splits), dim3(kAttnThreads), smem, s, qbuf, (const bf16*)k_cache, (const bf16*)v_cache, (const bf16*)proj, (bf16*)out, a);
   else DLI_LAUNCH("attn_ragged", attn_ragged_kernel<float>, dim3(rows, H, splits), dim3(kAttnThreads), smem, s, qbuf, (const float*)k_cache, (const float*)v_cache, (const float*)proj, (float*)out, a);
   if (splits > 1) {

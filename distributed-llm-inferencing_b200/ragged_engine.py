@@ -419,8 +419,8 @@ class RaggedEngine:
             self._cq = torch.empty(rows * max(max(m.q_rank for m in lat), 1), dtype=E, device=dev)
             self._q = torch.empty(rows * max(m.heads * (m.dim + m.rot_dims) for m in lat), dtype=E, device=dev)
             self._olat = torch.empty(rows * max(m.heads * m.kv_rank for m in lat), dtype=E, device=dev)
-            # partial sums of the key splits of decode rows (rows * heads * splits <= 8 * SMs + rows * heads)
-            self._apart = torch.empty((8 * self._sms + 16 * max(m.heads for m in lat)) * (max(m.kv_rank for m in lat) + 2),
+            # partial sums of the key splits of decode rows (rows * heads * splits <= 16 * SMs + 4 * rows * heads)
+            self._apart = torch.empty((16 * self._sms + 64 * max(m.heads for m in lat)) * (max(m.kv_rank for m in lat) + 2),
                                       dtype=f32, device=dev)
         att = [m for m in mx if m.kind == "attention"]
         if att:
@@ -907,7 +907,8 @@ class RaggedEngine:
         olat = self._olat[:rows * H * K].view(rows, H * K)
         # few rows (decode): every row's keys go to several CTAs, so that a long context is read by the whole GPU; the
         # count depends on the rows alone (a replayed graph keeps it while the contexts grow)
-        splits = max(1, min(32, (8 * self._sms) // (rows * H))) if rows <= 16 else 1
+        # (heads in fours: the shared-key/value kernel gives a CTA four heads of a row)
+        splits = max(1, min(64, (4 * self._sms) // (rows * ((H + 3) // 4)))) if rows <= 16 else 1
         part = self._apart if splits > 1 else None
         ops.attn_ragged(qbuf, pool, pool, None, olat, d_rent, d_ent, self.kv.page_table, H, 1, K + R, K, m.scale,
                         ldv=K + R, splits=splits, part=part, sink=sink)
