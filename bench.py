@@ -869,9 +869,12 @@ def fubepel_kernel_times(eng, spec, T, peaks):
         put(f"{tag}_delta_conv", timeit(lambda: ops.conv1d_act_ragged(proj, eng.slots[("ctail", li_d)], P["conv_w"], None, row_ent,
                                                                       ent, qkv, off["q"])), byt=rows * C * (eb + 4))
         ms = timeit(lambda: ops.delta_rule_ragged(qkv, proj, eng.slots[("S", li_d)], o, ent, m.heads, m.kv_heads, m.dim, m.vdim,
-                                                  off["b"], off["a"], P["a_log"], P["dt_bias"], m.scale, m.unit_eps), n=3, reps=3)
+                                                  off["b"], off["a"], P["a_log"], P["dt_bias"], m.scale, m.unit_eps, blocked=rows > 1), n=3, reps=3)
         if rows > 1:
-            put(f"{tag}_delta_rule", ms, fp32=rows * m.heads * m.dim * m.vdim * 6)   # three multiply-adds per state entry and token
+            put(f"{tag}_delta_rule_blocks", ms, fp32=rows * m.heads * m.dim * m.vdim * 6)   # three multiply-adds per state entry and token
+            ms = timeit(lambda: ops.delta_rule_ragged(qkv, proj, eng.slots[("S", li_d)], o, ent, m.heads, m.kv_heads, m.dim, m.vdim,
+                                                      off["b"], off["a"], P["a_log"], P["dt_bias"], m.scale, m.unit_eps), n=2, reps=2)
+            put(f"{tag}_delta_rule_row_by_row", ms, fp32=rows * m.heads * m.dim * m.vdim * 6)
         else:
             put(f"{tag}_delta_rule", ms, byt=2 * m.heads * m.dim * m.vdim * 4)
         put(f"{tag}_delta_head_norm_gate", timeit(lambda: ops.head_rmsnorm_gate(o, proj, P["out_norm"], mix, m.heads, m.vdim, 1e-6,

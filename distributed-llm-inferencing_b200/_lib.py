@@ -108,7 +108,7 @@ SIGNATURES = {
     "dli_token_side_act": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "dli_token_side_gate": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "dli_token_side": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _vp]),
-    "dli_delta_rule_ragged": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _f, _f, _i, _vp]),
+    "dli_delta_rule_ragged": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _f, _f, _i, _i, _vp]),
     "dli_head_rmsnorm_gate": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _i, _i, _i, _i, _vp]),
     "dli_mlstm_parallel_scratch_floats": (_sz, [_i, _i, _i, _i]),
     "dli_mlstm_ragged_parallel": (_i, [_vp, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i,

@@ -819,12 +819,13 @@ def token_side(x, ids, table, off: int, w_gate, w_proj, w, eps: float, he=None):
     return x
 
 
-def delta_rule_ragged(qkv, proj, St, o, ent, H, G, D, V, b_off, a_off, a_log, dt_bias, q_scale, unit_eps=1e-6):
+def delta_rule_ragged(qkv, proj, St, o, ent, H, G, D, V, b_off, a_off, a_log, dt_bias, q_scale, unit_eps=1e-6, blocked=False):
     """Gated delta rule over the rows of every entry.  qkv float32 [rows, 2*G*D + H*V] = q | k | v; St float32
-    [slots, H, V, D] (the transposed state) is advanced; o float32 [rows, H*V]."""
+    [slots, H, V, D] (the transposed state) is advanced; o float32 [rows, H*V].  blocked: 16 rows at a time (steps with portions
+    of prompts)."""
     _f32(qkv, St, o, a_log, dt_bias), _req(proj, proj.dtype), _i32(ent)
     _call("dli_delta_rule_ragged", 1, _p(qkv), _p(proj), _p(St), _p(o), _p(ent), ent.numel() // 4, H, G, D, V, qkv.shape[1],
-          proj.shape[1], b_off, a_off, _p(a_log), _p(dt_bias), float(q_scale), float(unit_eps), _dt(proj), _stream())
+          proj.shape[1], b_off, a_off, _p(a_log), _p(dt_bias), float(q_scale), float(unit_eps), int(bool(blocked)), _dt(proj), _stream())
     return o
 
 

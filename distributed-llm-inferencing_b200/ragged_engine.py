@@ -212,6 +212,9 @@ class RaggedEngine:
         self.moe_sel_max_rows = 8                  # up to this many rows a step reads only the chosen experts' weights ...
         self.moe_sel_share = 3.0                   # ... if they are at most 1/3 of all expert weights: the dense weight stream runs
                                                    # at ~0.63 of the HBM peak, the gathered one at ~0.2 (measured, 2048-wide)
+        self.delta_blocked = False                 # portions of prompts through the delta rule 16 rows at a time; off: row by row,
+                                                   # which is faster while one sequence's columns leave a warp per scheduler
+                                                   # (0.89 against 1.15 ms for 2 048 rows, 8 heads of 128 x 256)
         self.side_fused_max_rows = 16              # up to this many rows the per-layer token input is one kernel ...
         self.side_fused_max_bytes = 64 << 10       # ... if its two matrices are at most this large (else: weight streams)
         self.latent_expand_max_elems = 1 << 31     # scratch bound (4 GiB in bf16) of the per-head expansion of cached latents
@@ -732,7 +735,7 @@ class RaggedEngine:
         elif m.kind == "latent_attention":
             self._latent_attention(li, m, P, proj, mix, rows, views, tiles)
         elif m.kind == "delta":
-            self._delta(li, m, P, proj, mix, rows, views)
+            self._delta(li, m, P, proj, mix, rows, views, long_step and self.delta_blocked)
         else:
             raise ValueError(f"layer {li}: mixer {m.kind!r} has no output-normed form")
         self._lin(mix, P["wo"], y)
@@ -792,7 +795,7 @@ class RaggedEngine:
                             m.scale, chunk=m.chunk, window=m.window, sink=P["sink"], g_off=off["g"], cos_v=cv,
                             sin_v=sv, first=m.keep_first, splits=splits, part=self._apart_att if splits > 1 else None)
 
-    def _delta(self, li, m, P, proj, mix, rows, views):
+    def _delta(self, li, m, P, proj, mix, rows, views, long_step=False):
         """Gated delta rule: short convolutions and SiLU of q | k | v (fp32), the recurrence over the state slot, then
         the per-head norm, weight and SiLU gate."""
         d_tok, d_rent, d_ent, d_want, d_tiles = views
@@ -803,7 +806,7 @@ class RaggedEngine:
                               act=1)
         o = self._oscr[:rows * m.heads * m.vdim].view(rows, m.heads * m.vdim)
         ops.delta_rule_ragged(qkv, proj, self.slots[("S", li)], o, d_ent, m.heads, m.kv_heads, m.dim, m.vdim, off["b"],
-                              off["a"], P["a_log"], P["dt_bias"], m.scale, m.unit_eps)
+                              off["a"], P["a_log"], P["dt_bias"], m.scale, m.unit_eps, blocked=long_step)
         ops.head_rmsnorm_gate(o, proj, P["out_norm"], mix, m.heads, m.vdim, self.spec.eps, gate=1, g_off=off["g"])
 
     # ------------------------------------------------------------------ layers with side-by-side sublayers

@@ -590,12 +590,14 @@ int dli_token_side(float* x, const int32_t* ids, const void* table, const void* 
  * per value head h (query/key head h / (H/G)): q, k made unit vectors (x / sqrt(sum x^2 + unit_eps)), q times q_scale,
  * beta = sigmoid(proj[row, b_off + h]), g = exp(-exp(a_log[h]) * softplus(proj[row, a_off + h] + dt_bias[h]));
  * S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q -> o [rows, H*V] fp32.  St [slots, H, V, D] fp32 holds
- * the transposed state per sequence slot, read and advanced (an entry at position 0 starts from zero).
+ * the transposed state per sequence slot, read and advanced (an entry at position 0 starts from zero).  blocked != 0
+ * (steps with portions of prompts): 16 rows at a time, the read-outs of the old state for all of them at once and a
+ * 16-step substitution for u; 0: row by row (decode steps).  The two agree up to fp32 rounding.
  * dli_head_rmsnorm_gate: out [rows, H*V] = o / sqrt(mean_head(o^2) + eps) * w * act(proj[row, g_off + h*V + v]); w is
  * [H, V] (w_heads != 0) or [V] shared by the heads; gate 0 = none, 1 = SiLU, 2 = sigmoid. */
 int dli_delta_rule_ragged(const float* qkv, const void* proj, float* St, float* o, const int32_t* ent, int n_ent, int H,
                           int G, int D, int V, int ldx, int ldp, int b_off, int a_off, const float* a_log,
-                          const float* dt_bias, float q_scale, float unit_eps, int dt, dli_stream_t stream);
+                          const float* dt_bias, float q_scale, float unit_eps, int blocked, int dt, dli_stream_t stream);
 int dli_head_rmsnorm_gate(const float* o, const void* proj, const float* w, void* out, int rows, int H, int V, float eps,
                           int w_heads, int gate, int ldp, int g_off, int dt, dli_stream_t stream);
 

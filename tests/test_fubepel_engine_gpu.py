@@ -315,6 +315,15 @@ def test_decode_steps_replayed_as_a_graph_equal_eager_steps():
     assert torch.equal(outs[0], outs[1])
 
 
+def test_delta_rule_in_blocks_of_16_rows_through_the_engine():
+    """The engine's switch for portions of prompts: the block form against the oracle, in portions that end anywhere."""
+    cfg = cfg_c()
+    eng, sd = build(cfg, torch.float32)
+    eng.delta_blocked = True
+    toks = prompt(52, cfg["vocab"], 3)
+    assert rel_err(run_schedule(eng, toks, [17, 2, 16, 3]), R.forward(cfg, sd, toks)).max() < TOL32
+
+
 def test_per_layer_token_input_in_one_kernel_equals_its_separate_steps():
     """Few rows take the fused kernel, more rows two projections around the activation; both against the oracle."""
     cfg = cfg_a()

@@ -44,7 +44,7 @@ def views_of(entries):
             torch.tensor(tiles, dtype=torch.int32, device=DEV))
 
 
-def run_mixers(eng, us, cuts, tiles=False):
+def run_mixers(eng, us, cuts, tiles=False, delta_blocked=False):
     """us: per layer the mixer's input projection [T, columns] (made on the host), fed through the engine's mixer kernels
     in portions of the given sizes (then token by token) -> per layer the mixer's output before its out-projection."""
     T = us[0].shape[0]
@@ -69,7 +69,7 @@ def run_mixers(eng, us, cuts, tiles=False):
             elif m.kind == "latent_attention":
                 eng._latent_attention(li, m, P, proj, mix, n, views, tiles and n >= 16)
             else:
-                eng._delta(li, m, P, proj, mix, n, views)
+                eng._delta(li, m, P, proj, mix, n, views, long_step=delta_blocked and n >= 2)   # 16 rows at a time
             outs[li].append(mix.double().cpu())
         at += n
     return [torch.cat(o) for o in outs]
@@ -144,12 +144,14 @@ def test_latent_attention_sharp_scores_sink_and_another_layers_cache(cuts, tiles
     assert want0[:, :10].abs().max() < 1e-6 < want0[:, 10:].abs().max()     # the sink swallowed head 0
 
 
+@pytest.mark.parametrize("blocked", [False, True])
 @pytest.mark.parametrize("cuts", [[260], [1, 1, 2, 3], [64, 17, 2, 100], []])
 @pytest.mark.parametrize("shape", [(4, 2, 8, 6, 3), (2, 2, 40, 3, 1), (3, 1, 5, 33, 4)])
-def test_delta_rule_that_forgets_slowly(cuts, shape):
+def test_delta_rule_that_forgets_slowly(cuts, shape, blocked):
     """Decay ~0.999 per token: what the first tokens wrote is still in the read-out 260 tokens later, so a state that
     is lost or started from a slot's old content shows; value heads sharing query/key heads; a key size that leaves
-    lanes empty; more value columns than one CTA takes."""
+    lanes empty; more value columns than one CTA takes; row by row and 16 rows at a time (portions that end inside a block
+    of 16, blocks of one and two rows)."""
     H, G, D, V, conv = shape
     eng, cfg, sd = engine_of([(delta(heads=H, kv_heads=G, dim=D, vdim=V, conv=conv), None)], std=0.4)
     eng.layers[0]["a_log"].fill_(-6.0)
@@ -161,7 +163,7 @@ def test_delta_rule_that_forgets_slowly(cuts, shape):
     u = torch.cat([h @ P[k].T for k in ("q", "k", "v", "g", "b", "a")], 1)
     P["o"] = torch.eye(H * V, dtype=F64)
     want = R.gated_delta(h, P, cfg["layers"][0]["mixer"], 1e-5)
-    got = run_mixers(eng, [u], cuts)[0]
+    got = run_mixers(eng, [u], cuts, delta_blocked=blocked)[0]
     assert (got - want).abs().max() < 3e-4 * max(1.0, want.abs().max())
     # forgetting really is slow here: cutting the history changes the last outputs
     short = R.gated_delta(h[T // 2:], P, cfg["layers"][0]["mixer"], 1e-5)
