@@ -72,7 +72,7 @@ def spec_from_config(cfg: dict) -> HybridSpec:
                                 ff_limit=float(mlp["limit"]) if mlp else 0.0, ff_alpha=FF_ALPHA, side_dim=sdim,
                                 side_off=i * sdim))
     return HybridSpec(arch="fubepel", vocab=int(cfg["vocab"]), width=int(cfg["width"]), eps=float(cfg["norm"]["eps"]),
-                      taps=1, layers=layers, embed_scale=float(cfg["embedding"]["scale"]), norm_groups=1,
+                      taps=1, layers=layers, embed_scale=float((cfg.get("embedding") or {}).get("scale", 1.0)), norm_groups=1,
                       side_width=sdim * len(layers))
 
 

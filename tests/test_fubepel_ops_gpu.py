@@ -146,11 +146,11 @@ def test_latent_attention_sharp_scores_sink_and_another_layers_cache(cuts, tiles
 
 @pytest.mark.parametrize("blocked", [False, True])
 @pytest.mark.parametrize("cuts", [[260], [1, 1, 2, 3], [64, 17, 2, 100], []])
-@pytest.mark.parametrize("shape", [(4, 2, 8, 6, 3), (2, 2, 40, 3, 1), (3, 1, 5, 33, 4)])
+@pytest.mark.parametrize("shape", [(4, 2, 8, 6, 3), (2, 2, 40, 3, 1), (3, 1, 5, 33, 4), (1, 1, 168, 5, 2)])
 def test_delta_rule_that_forgets_slowly(cuts, shape, blocked):
     """Decay ~0.999 per token: what the first tokens wrote is still in the read-out 260 tokens later, so a state that
     is lost or started from a slot's old content shows; value heads sharing query/key heads; a key size that leaves
-    lanes empty; more value columns than one CTA takes; row by row and 16 rows at a time (portions that end inside a block
+    lanes empty; more value columns than one CTA takes; a key size beyond what a pass prefetches; row by row and 16 rows at a time (portions that end inside a block
     of 16, blocks of one and two rows)."""
     H, G, D, V, conv = shape
     eng, cfg, sd = engine_of([(delta(heads=H, kv_heads=G, dim=D, vdim=V, conv=conv), None)], std=0.4)
