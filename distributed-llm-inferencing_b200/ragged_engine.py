@@ -2,9 +2,12 @@
 
 ShardEngine (engine.py) serves uniform Llama / GPT-2 stacks on rectangular batches with a bf16 residual stream.
 This engine serves stacks described layer by layer (HybridSpec): every layer has a token mixer — softmax attention
-with its options, or a matrix-memory recurrent cell — and optionally a gated feed-forward; every sublayer is wrapped
-in a pre-norm and a post-norm with one weight each and reads its input through a short causal convolution; layers
-may share another layer's weights while keeping a cache / state of their own.  The residual stream, norms, rotation
+with its options, latent attention, or a recurrent cell with a matrix state (mLSTM, state-space, gated delta rule) —
+and optionally a feed-forward (dense or a mixture of experts).  Three layer styles: sublayers in sequence, each
+wrapped in a pre-norm and a post-norm with one weight and reading its input through a short causal convolution;
+mixer and feed-forward side by side on one grouped norm; sublayers that read the residual stream itself and are
+normed on their output only, followed by a per-layer token input.  Layers may share another layer's weights while
+keeping a cache / state of their own, or read another layer's cache.  The residual stream, norms, rotation
 angles, scores, softmax weights, convolution and recurrent state are fp32; projections run in the element type of the
 engine (bf16 on the tcgen05 / GEMV kernels of ops.linear, or float32 on the CUDA-core GEMM).
 
