@@ -70,7 +70,7 @@ SIGNATURES = {
     "dli_gemv_argmax_bf16": (_i, [_vp, _vp, _f, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _sz, _vp]),
     "dli_sample_bf16": (_i, [_vp, _i, _vp, _i, _i, _f, _i, _f, _vp, _vp, _vp, _vp, _i, _vp]),
     "dli_decode_advance": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _vp]),
-    "dli_embedding_f32": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _vp]),
+    "dli_embedding_f32": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _vp, _vp, _vp, _vp]),
     "dli_group_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _vp]),
     "dli_group_rmsnorm_conv_single": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _i, _vp]),
     "dli_residual_add2": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
@@ -86,24 +86,27 @@ SIGNATURES = {
     "dli_ssm_scan_ragged": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp, _vp, _vp, _i, _vp, _i, _vp, _i, _vp]),
     "dli_ssm_parallel_scratch_floats": (_sz, [_i, _i, _i, _i]),
     "dli_gated_group_rmsnorm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _i, _i, _vp]),
-    "dli_moe_route": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "dli_moe_route": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _vp]),
     "dli_moe_sel_supported": (_i, [_i, _i, _i, _i]),
-    "dli_moe_sel_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _f, _f, _vp]),
-    "dli_moe_act": (_i, [_vp, _vp, _vp, _i, _i, _i, _f, _i, _f, _f, _i, _i, _vp]),
+    "dli_moe_sel_bf16": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _f, _f, _i, _vp]),
+    "dli_moe_act": (_i, [_vp, _vp, _vp, _i, _i, _i, _f, _i, _f, _f, _i, _i, _i, _vp]),
     "dli_scalar_rmsnorm_f32": (_i, [_vp, _vp, _i, _i, _f, _f, _vp]),
     "dli_postnorm_add_norm": (_i, [_vp, _vp, _vp, _i, _i, _f, _f, _f, _i, _vp]),
     "dli_causal_conv_ragged": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "dli_postnorm_add_norm_conv_single": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _f, _f, _i, _vp]),
     "dli_gather_cast": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "dli_linear_any": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
-    "dli_silu_mul": (_i, [_vp, _vp, _i, _i, _i, _i, _vp]),
+    "dli_silu_mul": (_i, [_vp, _vp, _i, _i, _i, _i, _vp, _vp]),
     "dli_attn_prep_append": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i, _i,
-                                  _vp, _vp, _f, _vp, _vp, _vp, _vp, _i, _i, _vp]),
+                                  _vp, _vp, _f, _vp, _vp, _vp, _vp, _i, _i, _vp, _i, _vp]),
     "dli_attn_ragged": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp, _i,
-                             _i, _vp, _vp, _i, _i, _vp, _i, _vp]),
+                             _i, _vp, _vp, _i, _i, _vp, _i, _vp, _vp, _vp]),
     "dli_attn_ragged_tc_supported": (_i, [_i, _i, _i]),
     "dli_attn_ragged_tc": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp, _i,
-                                _i, _vp, _vp, _vp]),
+                                _i, _vp, _vp, _vp, _vp, _vp]),
+    "dli_layer_close": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i,
+                             _vp]),
+    "dli_token_shift_ragged": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "dli_postnorm_vec_add": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp]),
     "dli_token_side_act": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "dli_token_side_gate": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),

@@ -36,6 +36,7 @@ SOURCES = [
     "mamba2.cu",
     "moe.cu",
     "delta_rule.cu",
+    "prenorm_rows.cu",
 ]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]

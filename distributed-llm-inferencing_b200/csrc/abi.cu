@@ -69,7 +69,7 @@ extern "C" {
 
 const char* dli_last_error(void) { return dli::g_err; }
 
-int dli_version(void) { return 1007; }  // 1007: + gated delta rule, per-head norm with gate, post-norm with a weight vector, per-layer token input (delta_rule.cu, ragged_rows.cu); dli_attn_ragged / dli_attn_ragged_tc take `first`, dli_latent_prep / dli_latent_q_absorb take `halves` (and `ldq`), dli_embedding_f32 takes `xe`; + dli_linear_gated_act_bf16, dli_gemv_gated_act_bf16; 1006: + grouped norms, side-by-side sublayers, latent attention, state-space mixer, mixture of experts (latent_attn.cu, mamba2.cu, moe.cu); dli_embedding_f32 and dli_attn_ragged take more arguments; 1005: + ragged fp32-residual steps (ragged_rows.cu, attn_ragged.cu, mlstm.cu); 1004: + dli_gemm_qkv_rope_append_bf16 (1003: + dli_gemv_argmax_bf16; per-device kernel set-up)
+int dli_version(void) { return 1008; }  // 1008: + pre-norm layers with layer scale, token shift and depth average (prenorm_rows.cu); dli_embedding_f32 takes positions, dli_silu_mul a bias, dli_attn_prep_append a bias and q_only, dli_attn_ragged / dli_attn_ragged_tc a distance penalty, dli_moe_route groups / wscale / renorm, dli_moe_act / dli_moe_sel_bf16 a mode; 1007: + gated delta rule, per-head norm with gate, post-norm with a weight vector, per-layer token input (delta_rule.cu, ragged_rows.cu); dli_attn_ragged / dli_attn_ragged_tc take `first`, dli_latent_prep / dli_latent_q_absorb take `halves` (and `ldq`), dli_embedding_f32 takes `xe`; + dli_linear_gated_act_bf16, dli_gemv_gated_act_bf16; 1006: + grouped norms, side-by-side sublayers, latent attention, state-space mixer, mixture of experts (latent_attn.cu, mamba2.cu, moe.cu); dli_embedding_f32 and dli_attn_ragged take more arguments; 1005: + ragged fp32-residual steps (ragged_rows.cu, attn_ragged.cu, mlstm.cu); 1004: + dli_gemm_qkv_rope_append_bf16 (1003: + dli_gemv_argmax_bf16; per-device kernel set-up)
 
 int dli_set_pdl(int enable) {
   const int before = dli::pdl_enabled() ? 1 : 0;

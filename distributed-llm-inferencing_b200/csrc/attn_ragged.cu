@@ -9,7 +9,10 @@
 //   - a chunk mask (position i sees j <= i in its own chunk of `chunk` positions, counted from position 0) and/or
 //     a sliding window (j > i - window) that may also keep the sequence's first tokens (j < first) in view,
 //   - a sink: one more term exp(sink[h]) in the softmax denominator, without key or value,
-//   - an output gate: head h's output times sigmoid(gate[row, h]).
+//   - an output gate: head h's output times sigmoid(gate[row, h]),
+//   - biases on the q / k / v projections (added here, in fp32, before norm and rotation), a layer that only makes
+//     queries and reads ANOTHER layer's cached keys and values,
+//   - a distance penalty: r1[h] * ln(1 + r2[h] * (i - j)) is taken off the scaled score of query i and key j.
 // Scores, softmax weights and the accumulation are fp32; the cache holds E (bf16 or float).
 //
 // Step description as in ragged_rows.cu: row_ent[rows], ent[4 * n_ent] = (slot, first row, rows, first position);
@@ -42,6 +45,8 @@ struct AttnPrep {
   const float* cos_v;       // [positions, V/2] or NULL (values are cached as they are)
   const float* sin_v;
   int table_len;
+  const float* bias;        // [>= the projection's q / k / v columns] fp32 or NULL: added to the projection's columns
+  int q_only;               // 1: only the queries are made; keys and values are another layer's
 };
 
 // One CTA per row; each warp takes heads in turn: q heads -> qbuf (fp32, normed and rotated), key heads and value
@@ -58,16 +63,19 @@ attn_prep_append_kernel(const E* __restrict__ proj, float* __restrict__ qbuf, E*
   const int page = a.page_table[(size_t)e.x * a.max_pages + pos / a.page_size], off = pos % a.page_size;
   const E* pr = proj + (size_t)row * a.ldp;
   // grid.y spreads the heads of a row over CTAs (a decode row would otherwise walk all heads with four warps)
-  for (int item = blockIdx.y * 4 + warp; item < a.H + 2 * a.G; item += 4 * gridDim.y) {
+  const int n_items = a.q_only ? a.H : a.H + 2 * a.G;
+  for (int item = blockIdx.y * 4 + warp; item < n_items; item += 4 * gridDim.y) {
     if (item < a.H + a.G) {
       const bool is_q = item < a.H;
       const int hh = is_q ? item : item - a.H;
-      const E* src = pr + (is_q ? a.q_off : a.k_off) + hh * a.D;
+      const int col = (is_q ? a.q_off : a.k_off) + hh * a.D;
+      const E* src = pr + col;
+      const float* bs = a.bias ? a.bias + col : nullptr;
       const float* nw = is_q ? a.qn : a.kn;
       float r = 1.f;
       if (nw) {
         float ss = 0.f;
-        for (int c = lane; c < a.D; c += 32) { const float v = a_to_f(src[c]); ss += v * v; }
+        for (int c = lane; c < a.D; c += 32) { const float v = a_to_f(src[c]) + (bs ? bs[c] : 0.f); ss += v * v; }
         ss = warp_sum(ss);
         r = 1.f / sqrtf(ss / a.D + a.eps);
       }
@@ -75,6 +83,7 @@ attn_prep_append_kernel(const E* __restrict__ proj, float* __restrict__ qbuf, E*
       E* kd = kc + (((size_t)page * a.G + hh) * a.page_size + off) * a.D;
       for (int i = lane; i < a.D / 2; i += 32) {
         float u = a_to_f(src[2 * i]), v = a_to_f(src[2 * i + 1]);
+        if (bs) { u += bs[2 * i]; v += bs[2 * i + 1]; }
         if (nw) { u = u * r * nw[2 * i]; v = v * r * nw[2 * i + 1]; }
         if (a.cos_qk && 2 * i < a.rd) {
           const float c = a.cos_qk[(size_t)pos * (a.rd / 2) + i], s = a.sin_qk[(size_t)pos * (a.rd / 2) + i];
@@ -87,9 +96,11 @@ attn_prep_append_kernel(const E* __restrict__ proj, float* __restrict__ qbuf, E*
     } else {
       const int g = item - a.H - a.G;
       const E* src = pr + a.v_off + g * a.V;
+      const float* bs = a.bias ? a.bias + a.v_off + g * a.V : nullptr;
       E* vd = vc + (((size_t)page * a.G + g) * a.page_size + off) * a.V;
       for (int i = lane; i < a.V / 2; i += 32) {
         float u = a_to_f(src[2 * i]), v = a_to_f(src[2 * i + 1]);
+        if (bs) { u += bs[2 * i]; v += bs[2 * i + 1]; }
         if (a.cos_v) {
           const float c = a.cos_v[(size_t)pos * (a.V / 2) + i], s = a.sin_v[(size_t)pos * (a.V / 2) + i];
           const float u2 = u * c - v * s, v2 = v * c + u * s;
@@ -118,6 +129,8 @@ struct AttnRun {
                             // values are the leading part of the key rows of one shared pool)
   int splits;               // > 1: the keys of a row are dealt to `splits` CTAs (grid.z), whose partial sums
   float* part;              // [rows, H, splits, V + 2] (unnormalised output, maximum, denominator) a merge kernel adds
+  const float* r1;          // [H] or NULL: the distance penalty r1[h] * ln(1 + r2[h] * (i - j)) on the scaled scores
+  const float* r2;
 };
 
 // q (shared, fp32) . k row (global): 16-byte loads where the row allows them
@@ -201,6 +214,7 @@ attn_ragged_kernel(const float* __restrict__ qbuf, const E* __restrict__ kc, con
     je = min(pos, jb + per - 1);
   }
   auto key_pos = [&](int idx) { return idx < lo ? idx - shift : idx; };
+  const float pen1 = a.r1 ? a.r1[h] : 0.f, pen2 = a.r1 ? a.r2[h] : 0.f;
 
   const bool vec = attn_vec_values(a.V, a.ldv);
   const int groups = attn_value_groups(a.V, a.ldv);
@@ -223,15 +237,16 @@ attn_ragged_kernel(const float* __restrict__ qbuf, const E* __restrict__ kc, con
     float s = -INFINITY;
     {
       float dpart = 0.f;
+      int jp = pos;
       if (j <= je) {
-        const int jp = key_pos(j);
+        jp = key_pos(j);
         const E* kr = kc + (((size_t)pt[jp / a.page_size] * a.G + g) * a.page_size + jp % a.page_size) * a.D;
         const int len = a.D / tpk;
         dpart = dot_row(q + part * len, kr + part * len, len);
       }
       if (tpk > 1) dpart += __shfl_xor_sync(0xffffffffu, dpart, 1);
       if (tpk > 2) dpart += __shfl_xor_sync(0xffffffffu, dpart, 2);
-      if (j <= je && part == 0) s = dpart;
+      if (j <= je && part == 0) s = a.r1 ? dpart - pen1 * log1pf(pen2 * (float)(pos - jp)) : dpart;
     }
     // block maximum
     float mx = warp_max(s);
@@ -548,8 +563,8 @@ static int launch_shared_kv(const float* qbuf, const void* kc, const void* vc, v
 
 // Does a step of this shape take the shared-key/value kernel, and with how many heads per CTA (0: no)?
 static int shared_kv_heads(int H, int G, int D, int V, int ldv, int chunk, int window, int g_off, const float* cos_v, int dt,
-                           const void* kc, const void* vc) {
-  if (G != 1 || H < 2 || chunk > 0 || window > 0 || g_off >= 0 || cos_v) return 0;
+                           const void* kc, const void* vc, bool has_penalty) {
+  if (G != 1 || H < 2 || chunk > 0 || window > 0 || g_off >= 0 || cos_v || has_penalty) return 0;
   const size_t es = dt == 0 ? 2 : 4;
   if (D % 8 != 0 || !attn_vec_values(V, ldv) || (ldv * es) % (dt == 0 ? 8 : 16) != 0 || !aligned16(kc) ||
       (reinterpret_cast<uintptr_t>(vc) & 15u) != 0)
@@ -645,6 +660,9 @@ attn_ragged_tc_kernel(const float* __restrict__ qbuf, const bf16* __restrict__ k
   const float scale_log2 = a.scale * 1.4426950408889634f;
   // the sink is a score that is not scaled: in units of the raw dot product it is sink / scale
   const float m0 = a.sink ? a.sink[h] / a.scale : -INFINITY;
+  // the distance penalty in the softmax's base-2 exponent: r1 ln(1 + r2 d) log2(e) = r1 log2(1 + r2 d); the scores stay
+  // raw dot products, so it is taken off as pen / scale_log2
+  const float pen1 = a.r1 ? a.r1[h] / scale_log2 : 0.f, pen2 = a.r1 ? a.r2[h] : 0.f;
   float m_run[2] = {m0, m0};
   float l_run[2] = {(a.sink && t4 == 0) ? 1.f : 0.f, (a.sink && t4 == 0) ? 1.f : 0.f};
   float o[DV / 8][4];
@@ -687,6 +705,15 @@ attn_ragged_tc_kernel(const float* __restrict__ qbuf, const bf16* __restrict__ k
       }
     }
     const int tk0 = tile * kRtTile;
+    if (a.r1) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int x = 0; x < 4; ++x) {
+          const int dist = qabs[x >> 1] - (tk0 + j * 8 + 2 * t4 + (x & 1));
+          s[j][x] -= pen1 * __log2f(fmaf(pen2, (float)max(dist, 0), 1.f));
+        }
+    }
     if (tk0 + kRtTile - 1 > p0 || tk0 < row_lo(p_last)) {  // the tile touches the diagonal or a lower bound
 #pragma unroll
       for (int j = 0; j < 8; ++j)
@@ -785,17 +812,17 @@ int dli_attn_prep_append(const void* proj, float* qbuf, void* k_cache, void* v_c
                          const int32_t* ent, const int32_t* page_table, int max_pages, int page_size, int rows, int H,
                          int G, int D, int V, int rd, int ldp, int q_off, int k_off, int v_off, const float* q_norm,
                          const float* k_norm, float eps, const float* cos_qk, const float* sin_qk, const float* cos_v,
-                         const float* sin_v, int table_len, int dt, dli_stream_t stream) {
-  DLI_CHECK_ARG(proj && qbuf && k_cache && v_cache && row_ent && ent && page_table, "dli_attn_prep_append: null pointer");
+                         const float* sin_v, int table_len, int dt, const float* bias, int q_only, dli_stream_t stream) {
+  DLI_CHECK_ARG(proj && qbuf && (q_only || (k_cache && v_cache)) && row_ent && ent && page_table, "dli_attn_prep_append: null pointer");
   DLI_CHECK_ARG(H > 0 && G > 0 && H % G == 0 && D > 0 && V > 0 && D % 2 == 0 && V % 2 == 0 && rd % 2 == 0 && rd <= D,
                 "dli_attn_prep_append: H=%d G=%d D=%d V=%d rd=%d (H %% G == 0, even sizes, rd <= D)", H, G, D, V, rd);
   DLI_CHECK_ARG((reinterpret_cast<uintptr_t>(ent) & 15u) == 0, "dli_attn_prep_append: ent must be 16-byte aligned");
   DLI_CHECK_ARG(dt == 0 || dt == 1, "element type %d: 0 = bf16, 1 = float", dt);
   if (rows <= 0) return DLI_OK;
   AttnPrep a{row_ent, ent, page_table, max_pages, page_size, H, G, D, V, rd, ldp, q_off, k_off, v_off, q_norm, k_norm,
-             eps, (rd > 0 ? cos_qk : nullptr), sin_qk, cos_v, sin_v, table_len};
+             eps, (rd > 0 ? cos_qk : nullptr), sin_qk, cos_v, sin_v, table_len, bias, q_only ? 1 : 0};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int items = H + 2 * G;
+  const int items = q_only ? H : H + 2 * G;
   const dim3 pgrid(rows, rows <= 64 ? (items + 3) / 4 : 1);
   if (dt == 0) DLI_LAUNCH("attn_prep_append", attn_prep_append_kernel<bf16>, pgrid, dim3(128), 0, s, (const bf16*)proj, qbuf, (bf16*)k_cache, (bf16*)v_cache, a);
   else DLI_LAUNCH("attn_prep_append", attn_prep_append_kernel<float>, pgrid, dim3(128), 0, s, (const float*)proj, qbuf, (float*)k_cache, (float*)v_cache, a);
@@ -806,7 +833,7 @@ int dli_attn_ragged(const float* qbuf, const void* k_cache, const void* v_cache,
                     const int32_t* row_ent, const int32_t* ent, const int32_t* page_table, int max_pages, int page_size,
                     int rows, int H, int G, int D, int V, float scale, int chunk, int window, int first, const float* sink,
                     int ldp, int g_off, const float* cos_v, const float* sin_v, int ldv, int splits, float* part, int dt,
-                    dli_stream_t stream) {
+                    const float* r1, const float* r2, dli_stream_t stream) {
   DLI_CHECK_ARG(qbuf && k_cache && v_cache && out && row_ent && ent && page_table, "dli_attn_ragged: null pointer");
   DLI_CHECK_ARG(splits >= 1 && splits <= 64 && (splits == 1 || part), "dli_attn_ragged: %d key splits (1..64, with scratch)", splits);
   DLI_CHECK_ARG(ldv == 0 || ldv >= V, "dli_attn_ragged: value row stride %d is below the value size %d", ldv, V);
@@ -817,13 +844,14 @@ int dli_attn_ragged(const float* qbuf, const void* k_cache, const void* v_cache,
   DLI_CHECK_ARG(dt == 0 || dt == 1, "element type %d: 0 = bf16, 1 = float", dt);
   if (rows <= 0) return DLI_OK;
   DLI_CHECK_ARG(first >= 0, "dli_attn_ragged: %d kept first positions", first);
+  DLI_CHECK_ARG((r1 == nullptr) == (r2 == nullptr), "dli_attn_ragged: the distance penalty needs both r1 and r2");
   AttnRun a{row_ent, ent, page_table, max_pages, page_size, H, G, D, V, scale, chunk, window, first, sink, ldp, g_off, cos_v,
-            sin_v, ldv ? ldv : V, splits, part};
+            sin_v, ldv ? ldv : V, splits, part, r1, r2};
   const int groups = attn_value_groups(V, ldv ? ldv : V);
   const size_t smem = sizeof(float) * (D + kAttnThreads + 8 + (size_t)groups * V);
   DLI_CHECK_ARG(smem <= 48 * 1024, "dli_attn_ragged: key size %d needs %zu bytes of shared memory", D, smem);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int hpc = shared_kv_heads(H, G, D, V, ldv ? ldv : V, chunk, window, g_off, cos_v, dt, k_cache, v_cache);
+  const int hpc = shared_kv_heads(H, G, D, V, ldv ? ldv : V, chunk, window, g_off, cos_v, dt, k_cache, v_cache, r1 != nullptr);
   if (hpc) {
     int rc;
     if (dt == 0) rc = hpc == 4 ? launch_shared_kv<bf16, 4>(qbuf, k_cache, v_cache, out, rows, a, s)
@@ -849,7 +877,8 @@ int dli_attn_ragged_tc_supported(int D, int V, int dt) {
 int dli_attn_ragged_tc(const float* qbuf, const void* k_cache, const void* v_cache, const void* proj, void* out,
                        const int32_t* ent, const int32_t* tiles, int n_tiles, const int32_t* page_table, int max_pages,
                        int page_size, int H, int G, int D, int V, float scale, int chunk, int window, int first,
-                       const float* sink, int ldp, int g_off, const float* cos_v, const float* sin_v, dli_stream_t stream) {
+                       const float* sink, int ldp, int g_off, const float* cos_v, const float* sin_v, const float* r1,
+                       const float* r2, dli_stream_t stream) {
   DLI_CHECK_ARG(qbuf && k_cache && v_cache && out && ent && tiles && page_table, "dli_attn_ragged_tc: null pointer");
   DLI_CHECK_ARG(g_off < 0 || proj, "dli_attn_ragged_tc: a gate needs the projection rows");
   DLI_CHECK_ARG(H > 0 && G > 0 && H % G == 0 && scale > 0.f, "dli_attn_ragged_tc: H=%d G=%d scale=%g", H, G, scale);
@@ -857,7 +886,8 @@ int dli_attn_ragged_tc(const float* qbuf, const void* k_cache, const void* v_cac
     return dli::fail(DLI_ERR_UNSUPPORTED, "dli_attn_ragged_tc: key size %d with value size %d has no tensor-core tile", D, V);
   if (n_tiles <= 0) return DLI_OK;
   DLI_CHECK_ARG(first >= 0, "dli_attn_ragged_tc: %d kept first positions", first);
-  AttnRun a{nullptr, ent, page_table, max_pages, page_size, H, G, D, V, scale, chunk, window, first, sink, ldp, g_off, cos_v, sin_v, V, 1, nullptr};
+  DLI_CHECK_ARG((r1 == nullptr) == (r2 == nullptr), "dli_attn_ragged_tc: the distance penalty needs both r1 and r2");
+  AttnRun a{nullptr, ent, page_table, max_pages, page_size, H, G, D, V, scale, chunk, window, first, sink, ldp, g_off, cos_v, sin_v, V, 1, nullptr, r1, r2};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (D == 64 && V == 64) return launch_ragged_tc<64, 64>(qbuf, k_cache, v_cache, proj, out, tiles, n_tiles, a, s);
   if (D == 128 && V == 128) return launch_ragged_tc<128, 128>(qbuf, k_cache, v_cache, proj, out, tiles, n_tiles, a, s);

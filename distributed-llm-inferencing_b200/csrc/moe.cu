@@ -1,7 +1,10 @@
 // Mixture-of-experts feed-forward for a RAGGED step: the router and the expert activation.
 //
 //   dli_moe_route   logits z = W_r h (fp32), scores s = softmax(z) over all router outputs; the `top` outputs with
-//                   the largest s + correction are chosen; their weights are s / (sum of the chosen s + 1e-20).
+//                   the largest s + correction are chosen; their weights are s / (sum of the chosen s + 1e-20), or,
+//                   without renormalisation, s itself, in both cases times `wscale`.  With groups > 1 the outputs form
+//                   that many equal groups of neighbours, a group's score is its largest s + correction, and only
+//                   outputs of the `keep` best groups can be chosen.
 //                   The last n_identity router outputs are experts that return their input: their weights are
 //                   summed into idw[row].  Written: the dense weight row wts[row, 0 .. n_real) (0 for experts that
 //                   were not chosen), idw[row], and the choice itself (sel_idx / sel_w [row, top]).
@@ -9,7 +12,7 @@
 //                   g = min(g, limit), u = clamp(u, -limit, limit), a = g * sigmoid(alpha g) * (u + 1), times the
 //                   expert's routing weight, so that ONE down projection over the concatenated experts is the
 //                   weighted sum of their outputs.  A shared expert (its own size and limit, weight 1) is the last
-//                   block.
+//                   block.  mode 1: experts without a gate, a = max(u, 0)^2 on the stacked up projections.
 #include <math.h>
 
 #include "common.cuh"
@@ -27,9 +30,11 @@ template <> __device__ __forceinline__ bf16 x_from_f<bf16>(float v) { return __f
 __global__ void __launch_bounds__(512)
 moe_route_kernel(const float* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ corr,
                  float* __restrict__ wts, float* __restrict__ idw, int32_t* __restrict__ sel_idx,
-                 float* __restrict__ sel_w, int d, int n_out, int n_real, int top) {
-  extern __shared__ float zs[];  // [n_out] scores, [n_out] choice scores
+                 float* __restrict__ sel_w, int d, int n_out, int n_real, int top, int groups, int keep, float wscale,
+                 int renorm) {
+  extern __shared__ float zs[];  // [n_out] scores, [n_out] choice scores, [groups] group scores
   float* cs = zs + n_out;
+  float* gm = cs + n_out;
   pdl_wait();
   pdl_trigger();
   const size_t row = blockIdx.x;
@@ -67,6 +72,34 @@ moe_route_kernel(const float* __restrict__ h, const float* __restrict__ wr, cons
     if (o < n_real) wts[row * n_real + o] = 0.f;
   }
   __syncwarp();
+  if (groups > 1) {
+    // a group's score is its largest choice score; the groups that are not among the `keep` best leave the choice
+    const int per = n_out / groups;
+    for (int g = lane; g < groups; g += 32) {
+      float b = -INFINITY;
+      for (int o = g * per; o < (g + 1) * per; ++o) b = fmaxf(b, cs[o]);
+      gm[g] = b;
+    }
+    __syncwarp();
+    for (int k = 0; k < keep; ++k) {
+      float best = -INFINITY;
+      int bi = 0x7fffffff;
+      for (int g = lane; g < groups; g += 32) {
+        const float c = gm[g];
+        if (c > best && c != INFINITY) { best = c; bi = g; }
+      }
+      for (int off = 16; off > 0; off >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, off);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
+        if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+      }
+      if (lane == 0 && bi < groups) gm[bi] = INFINITY;  // kept
+      __syncwarp();
+    }
+    for (int o = lane; o < n_out; o += 32)
+      if (gm[o / per] != INFINITY) cs[o] = -INFINITY;
+    __syncwarp();
+  }
   // the `top` largest choice scores, one at a time (lowest index wins a tie)
   float chosen_sum = 0.f;
   for (int k = 0; k < top; ++k) {
@@ -81,6 +114,7 @@ moe_route_kernel(const float* __restrict__ h, const float* __restrict__ wr, cons
       const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
       if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
     }
+    if (bi >= n_out) bi = 0;  // fewer candidates than `top` (every score -inf or NaN): stay inside the row
     if (lane == 0) {
       cs[bi] = -INFINITY;
       sel_idx[row * top + k] = bi;
@@ -88,7 +122,7 @@ moe_route_kernel(const float* __restrict__ h, const float* __restrict__ wr, cons
     chosen_sum += zs[bi];
     __syncwarp();
   }
-  const float inv = 1.f / (chosen_sum + 1e-20f);
+  const float inv = (renorm ? 1.f / (chosen_sum + 1e-20f) : 1.f) * wscale;
   if (lane == 0) {
     float ident = 0.f;
     for (int k = 0; k < top; ++k) {
@@ -109,6 +143,7 @@ struct MoeAct {
   float limit_s;
   float alpha;              // g * sigmoid(alpha * g)
   int ld;                   // row stride of gu
+  int mode;                 // 0: clamped gated form; 1: no gate, max(u, 0)^2, columns [e*ff, +ff) of gu (shared: after them)
 };
 
 // act[row, e*ff + f] and act[row, n_exp*ff + f] (shared); a row's channels go to one CTA, or to several for few rows.
@@ -123,6 +158,16 @@ moe_act_kernel(const E* __restrict__ gu, const float* __restrict__ wts, E* __res
   E* out = act + row * F;
   for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < F; i += blockDim.x * gridDim.y) {
     float gv, uv, lim, wt;
+    if (a.mode == 1) {
+      wt = 1.f;
+      if (i < a.n_exp * a.ff) {
+        wt = wts[row * a.n_exp + i / a.ff];
+        if (wt == 0.f) { out[i] = x_from_f<E>(0.f); continue; }
+      }
+      const float u = fmaxf(x_to_f(g[i]), 0.f);
+      out[i] = x_from_f<E>(u * u * wt);
+      continue;
+    }
     if (i < a.n_exp * a.ff) {
       const int e = i / a.ff, f = i - e * a.ff;
       wt = wts[row * a.n_exp + e];
@@ -183,6 +228,35 @@ moe_sel_act_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w_gu, co
   __syncthreads();
   const float wt = shared ? 1.f : sel_w[row * top + k];
   const float lim = shared ? a.limit_s : a.limit;
+  if (a.mode == 1) {
+    // experts without a gate: one weight row per output, two outputs at a time
+    const bf16* base1 = w_gu + (size_t)e * a.ff * d;
+    for (int f = f0; f < min(f0 + kSelPerWarp, ff); f += 2) {
+      const int f1 = min(f + 1, ff - 1);
+      const bf16* r0 = base1 + (size_t)f * d;
+      const bf16* r1 = base1 + (size_t)f1 * d;
+      float u0 = 0.f, u1 = 0.f;
+      int c = lane * 8;
+      for (; c + 768 < d; c += 1024) {  // eight 16-byte loads in flight per lane
+        uint4 w0[4], w1[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { w0[i] = ld_stream_16B(r0 + c + i * 256); w1[i] = ld_stream_16B(r1 + c + i * 256); }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { u0 += dot8(w0[i], xs + c + i * 256); u1 += dot8(w1[i], xs + c + i * 256); }
+      }
+      for (; c < d; c += 256) {
+        u0 += dot8(ld_stream_16B(r0 + c), xs + c);
+        u1 += dot8(ld_stream_16B(r1 + c), xs + c);
+      }
+      u0 = warp_sum(u0); u1 = warp_sum(u1);
+      if (lane < 2 && f + lane < ff) {
+        float u = lane ? u1 : u0;
+        u = fmaxf(__bfloat162float(__float2bfloat16_rn(u)), 0.f);  // the projection's output is a bf16 row, as on the dense path
+        out[f + lane] = __float2bfloat16_rn(u * u * wt);
+      }
+    }
+    return;
+  }
   const bf16* base = w_gu + (size_t)e * 2 * a.ff * d;  // the shared expert's block follows the n_exp routed ones
   for (int f = f0; f < min(f0 + kSelPerWarp, ff); f += 2) {
     // two outputs at a time: the gate and up rows of both are streamed together (eight 16-byte loads in flight per lane)
@@ -268,24 +342,29 @@ using namespace dli;
 extern "C" {
 
 int dli_moe_route(const float* h, const float* w_router, const float* correction, float* wts, float* idw, int32_t* sel_idx,
-                  float* sel_w, int rows, int d, int n_out, int n_real, int top, dli_stream_t stream) {
+                  float* sel_w, int rows, int d, int n_out, int n_real, int top, int groups, int keep, float wscale,
+                  int renorm, dli_stream_t stream) {
   DLI_CHECK_ARG(h && w_router && wts && idw && sel_idx && sel_w, "dli_moe_route: null pointer");
+  if (groups < 1) groups = 1;
+  DLI_CHECK_ARG(groups == 1 || (n_out % groups == 0 && keep >= 1 && keep <= groups && keep * (n_out / groups) >= top),
+                "dli_moe_route: %d router outputs in %d groups of which %d are kept, top %d", n_out, groups, keep, top);
   DLI_CHECK_ARG(d > 0 && n_out > 0 && n_real >= 0 && n_real <= n_out && top > 0 && top <= n_out && n_out <= 4096,
                 "dli_moe_route: %d router outputs (%d real experts), top %d", n_out, n_real, top);
   if (rows <= 0) return DLI_OK;
-  DLI_LAUNCH("moe_route", moe_route_kernel, dim3(rows), dim3(rows <= 64 ? 512 : 256), (size_t)2 * n_out * sizeof(float),
-             static_cast<cudaStream_t>(stream), h, w_router, correction, wts, idw, sel_idx, sel_w, d, n_out, n_real, top);
+  DLI_LAUNCH("moe_route", moe_route_kernel, dim3(rows), dim3(rows <= 64 ? 512 : 256), (size_t)(2 * n_out + groups) * sizeof(float),
+             static_cast<cudaStream_t>(stream), h, w_router, correction, wts, idw, sel_idx, sel_w, d, n_out, n_real, top,
+             groups, keep, wscale, renorm);
   return DLI_OK;
 }
 
 int dli_moe_act(const void* gu, const float* wts, void* act, int rows, int n_exp, int ff, float limit, int ff_s,
-                float limit_s, float alpha, int ld, int dt, dli_stream_t stream) {
+                float limit_s, float alpha, int ld, int dt, int mode, dli_stream_t stream) {
   DLI_CHECK_ARG(gu && act && (wts || n_exp == 0) && n_exp >= 0 && ff >= 0 && ff_s >= 0 && n_exp * ff + ff_s > 0 &&
-                    ld >= 2 * (n_exp * ff + ff_s),
+                    (mode == 0 || mode == 1) && ld >= (mode == 1 ? 1 : 2) * (n_exp * ff + ff_s),
                 "dli_moe_act: null pointer or bad shape");
   DLI_CHECK_ARG(dt == 0 || dt == 1, "element type %d: 0 = bf16, 1 = float", dt);
   if (rows <= 0) return DLI_OK;
-  MoeAct a{n_exp, ff, limit, ff_s, limit_s, alpha, ld};
+  MoeAct a{n_exp, ff, limit, ff_s, limit_s, alpha, ld, mode};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int gy = rows <= 64 ? min(64, (n_exp * ff + ff_s + 255) / 256) : 1;  // few rows: a row's channels over several CTAs
   if (dt == 0) DLI_LAUNCH("moe_act", moe_act_kernel<bf16>, dim3(rows, gy), dim3(256), 0, s, (const bf16*)gu, wts, (bf16*)act, a);
@@ -299,12 +378,12 @@ int dli_moe_sel_supported(int d, int ff, int ff_s, int top) {
 
 int dli_moe_sel_bf16(const void* x, const void* w_gu, const void* w_down, const int32_t* sel_idx, const float* sel_w,
                      void* act_sel, void* y, int rows, int d, int n_exp, int top, int ff, float limit, int ff_s,
-                     float limit_s, float alpha, dli_stream_t stream) {
-  DLI_CHECK_ARG(x && w_gu && w_down && sel_idx && sel_w && act_sel && y, "dli_moe_sel_bf16: null pointer");
+                     float limit_s, float alpha, int mode, dli_stream_t stream) {
+  DLI_CHECK_ARG(x && w_gu && w_down && sel_idx && sel_w && act_sel && y && (mode == 0 || mode == 1), "dli_moe_sel_bf16: null pointer");
   DLI_CHECK_ARG(n_exp >= 0 && top >= 0 && dli_moe_sel_supported(d, ff, ff_s, top) && aligned16(w_gu) && aligned16(w_down),
                 "dli_moe_sel_bf16: sizes d=%d ff=%d ff_s=%d must be multiples of 8 and fit shared memory", d, ff, ff_s);
   if (rows <= 0) return DLI_OK;
-  MoeAct a{n_exp, ff, limit, ff_s, limit_s, alpha, 0};
+  MoeAct a{n_exp, ff, limit, ff_s, limit_s, alpha, 0, mode};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   static PerDeviceOnce once_a, once_d;
   DLI_ONCE_PER_DEVICE(once_a, dev, DLI_CUDA_CALL(cudaFuncSetAttribute(moe_sel_act_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024)));

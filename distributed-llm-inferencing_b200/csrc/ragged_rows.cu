@@ -31,18 +31,31 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   return t;
 }
 
-// x[row] = table[ids[row]] as fp32 (the residual stream starts in fp32).
+// x[row] = table[ids[row]] * scale as fp32 (the residual stream starts in fp32).  With inv_freq [ceil(d/2)] a sinusoidal
+// position vector is added: channel 2i gets sin(p * inv_freq[i]), channel 2i+1 the cosine, p the row's position in its
+// sequence (from row_ent / ent), angle and functions in fp32.
 template <typename E>
 __global__ void __launch_bounds__(1024)
 embedding_f32_kernel(const int32_t* __restrict__ ids, const E* __restrict__ table, float* __restrict__ x,
-                     float* __restrict__ x2, E* __restrict__ xe, int d, int vocab, float scale) {
+                     float* __restrict__ x2, E* __restrict__ xe, int d, int vocab, float scale,
+                     const int32_t* __restrict__ row_ent, const int32_t* __restrict__ ent,
+                     const float* __restrict__ inv_freq) {
   pdl_wait();
   pdl_trigger();
   const size_t row = blockIdx.x;
   int id = ids[row];
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+  float pos = 0.f;
+  if (inv_freq) {
+    const int4 e = reinterpret_cast<const int4*>(ent)[row_ent[row]];
+    pos = (float)(e.w + ((int)row - e.y));
+  }
   for (int c = threadIdx.x; c < d; c += blockDim.x) {
-    const float v = to_f(table[(size_t)id * d + c]) * scale;
+    float v = to_f(table[(size_t)id * d + c]) * scale;
+    if (inv_freq) {
+      const float ang = pos * inv_freq[c >> 1];
+      v += (c & 1) ? cosf(ang) : sinf(ang);
+    }
     x[row * d + c] = v;
     if (x2) x2[row * d + c] = v;
     if (xe) xe[row * d + c] = from_f<E>(v);
@@ -393,15 +406,16 @@ linear_any_kernel(const E* __restrict__ x, const E* __restrict__ w, O* __restric
     }
 }
 
-// act[m, f] = silu(gu[m, f]) * gu[m, F + f]
+// act[m, f] = silu(gu[m, f] + b[f]) * (gu[m, F + f] + b[F + f]); bias [2F] fp32 or NULL
 template <typename E>
 __global__ void __launch_bounds__(256)
-silu_mul_kernel(const E* __restrict__ gu, E* __restrict__ act, int F, int ld) {
+silu_mul_kernel(const E* __restrict__ gu, E* __restrict__ act, int F, int ld, const float* __restrict__ bias) {
   pdl_wait();
   pdl_trigger();
   const size_t m = blockIdx.x;
-  for (int f = threadIdx.x; f < F; f += blockDim.x) {
-    const float g = to_f(gu[m * ld + f]), u = to_f(gu[m * ld + F + f]);
+  for (int f = blockIdx.y * blockDim.x + threadIdx.x; f < F; f += blockDim.x * gridDim.y) {
+    float g = to_f(gu[m * ld + f]), u = to_f(gu[m * ld + F + f]);
+    if (bias) { g += bias[f]; u += bias[F + f]; }
     act[m * F + f] = from_f<E>(to_f(from_f<E>(silu_f(g))) * u);
   }
 }
@@ -536,13 +550,16 @@ static inline int row_threads(int rows, int d) { return (rows <= 64 && d >= 2048
 extern "C" {
 
 int dli_embedding_f32(const int32_t* ids, const void* table, float* x, float* x2, void* xe, int rows, int d, int vocab,
-                      float scale, int dt, dli_stream_t stream) {
+                      float scale, int dt, const int32_t* row_ent, const int32_t* ent, const float* inv_freq,
+                      dli_stream_t stream) {
   DLI_CHECK_ARG(ids && table && x && d > 0 && vocab > 0, "dli_embedding_f32: null pointer or empty shape");
+  DLI_CHECK_ARG(!inv_freq || (row_ent && ent && (reinterpret_cast<uintptr_t>(ent) & 15u) == 0),
+                "dli_embedding_f32: positions need row_ent and a 16-byte aligned ent");
   DT_CHECK(dt);
   if (rows <= 0) return DLI_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dt == 0) DLI_LAUNCH("embedding_f32", embedding_f32_kernel<bf16>, dim3(rows), dim3(row_threads(rows, d)), 0, s, ids, (const bf16*)table, x, x2, (bf16*)xe, d, vocab, scale);
-  else DLI_LAUNCH("embedding_f32", embedding_f32_kernel<float>, dim3(rows), dim3(row_threads(rows, d)), 0, s, ids, (const float*)table, x, x2, (float*)xe, d, vocab, scale);
+  if (dt == 0) DLI_LAUNCH("embedding_f32", embedding_f32_kernel<bf16>, dim3(rows), dim3(row_threads(rows, d)), 0, s, ids, (const bf16*)table, x, x2, (bf16*)xe, d, vocab, scale, row_ent, ent, inv_freq);
+  else DLI_LAUNCH("embedding_f32", embedding_f32_kernel<float>, dim3(rows), dim3(row_threads(rows, d)), 0, s, ids, (const float*)table, x, x2, (float*)xe, d, vocab, scale, row_ent, ent, inv_freq);
   return DLI_OK;
 }
 
@@ -680,13 +697,14 @@ int dli_linear_any(const void* x, const void* w, void* y, int M, int N, int K, i
   return DLI_OK;
 }
 
-int dli_silu_mul(const void* gu, void* act, int M, int F, int ld, int dt, dli_stream_t stream) {
+int dli_silu_mul(const void* gu, void* act, int M, int F, int ld, int dt, const float* bias, dli_stream_t stream) {
   DLI_CHECK_ARG(gu && act && F > 0 && ld >= 2 * F, "dli_silu_mul: null pointer or bad shape");
   DT_CHECK(dt);
   if (M <= 0) return DLI_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dt == 0) DLI_LAUNCH("silu_mul", silu_mul_kernel<bf16>, dim3(M), dim3(256), 0, s, (const bf16*)gu, (bf16*)act, F, ld);
-  else DLI_LAUNCH("silu_mul", silu_mul_kernel<float>, dim3(M), dim3(256), 0, s, (const float*)gu, (float*)act, F, ld);
+  const dim3 grid(M, M <= 64 ? (F + 1023) / 1024 : 1);  // few rows: a row's channels go to several CTAs
+  if (dt == 0) DLI_LAUNCH("silu_mul", silu_mul_kernel<bf16>, grid, dim3(256), 0, s, (const bf16*)gu, (bf16*)act, F, ld, bias);
+  else DLI_LAUNCH("silu_mul", silu_mul_kernel<float>, grid, dim3(256), 0, s, (const float*)gu, (float*)act, F, ld, bias);
   return DLI_OK;
 }
 

@@ -1,8 +1,8 @@
 """Model registry: which engine serves a model directory.
 
 config.json decides: `model_type` llama / mistral / gpt2 -> engine.ShardEngine (uniform stacks, Hugging Face tensor
-names); `architecture` Sokevik, Togalorn or Fubepel -> ragged_engine.RaggedEngine with the layer list that sokevik.py /
-togalorn.py / fubepel.py read from the configuration.  The worker, the trace replayer (bin/trace_run) and bench.py all come
+names); `architecture` Sokevik, Togalorn, Fubepel or Gimudra -> ragged_engine.RaggedEngine with the layer list that sokevik.py /
+togalorn.py / fubepel.py / gimudra.py read from the configuration.  The worker, the trace replayer (bin/trace_run) and bench.py all come
 through here.
 """
 from __future__ import annotations
@@ -21,7 +21,7 @@ def read_config(path: str) -> dict:
 
 # designs described layer by layer, served by RaggedEngine: architecture -> module with spec_from_config,
 # model_tensors and random_state_dict
-LAYERWISE = {"Sokevik": "sokevik", "Togalorn": "togalorn", "Fubepel": "fubepel"}
+LAYERWISE = {"Sokevik": "sokevik", "Togalorn": "togalorn", "Fubepel": "fubepel", "Gimudra": "gimudra"}
 
 
 def family(cfg: dict) -> str:

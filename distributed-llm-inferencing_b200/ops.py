@@ -482,12 +482,15 @@ def _i32(*ts):
         _req(t, torch.int32)
 
 
-def embedding_f32(ids, table, out, scale: float = 1.0, out2=None, out_e=None):
+def embedding_f32(ids, table, out, scale: float = 1.0, out2=None, out_e=None, row_ent=None, ent=None, inv_freq=None):
     """ids int32 [rows]; table [V, d] bf16 / float -> out float32 [rows, d] = table[ids] * scale (out2: a second copy;
-    out_e: a copy in the table's element type)."""
-    _i32(ids), _req(table, table.dtype), _f32(out, out2), _req(out_e, table.dtype)
+    out_e: a copy in the table's element type).  inv_freq float32 [ceil(d/2)] with row_ent / ent: plus the sinusoidal
+    position vector (sin(p f_i) at channel 2i, cos(p f_i) at 2i+1)."""
+    _i32(ids, row_ent, ent), _req(table, table.dtype), _f32(out, out2, inv_freq), _req(out_e, table.dtype)
+    if inv_freq is not None and inv_freq.numel() < (table.shape[1] + 1) // 2:
+        raise ValueError("embedding_f32: one frequency per pair of channels")
     _call("dli_embedding_f32", 1, _p(ids), _p(table), _p(out), _p(out2), _p(out_e), ids.numel(), table.shape[1],
-          table.shape[0], float(scale), _dt(table), _stream())
+          table.shape[0], float(scale), _dt(table), _p(row_ent), _p(ent), _p(inv_freq), _stream())
     return out
 
 
@@ -572,37 +575,41 @@ def linear_any(x, w, out):
     return out
 
 
-def silu_mul(gu, out):
-    """out[m, f] = silu(gu[m, f]) * gu[m, F + f]."""
-    _req(gu, gu.dtype), _req(out, gu.dtype)
-    _call("dli_silu_mul", 1, _p(gu), _p(out), gu.shape[0], out.shape[1], gu.shape[1], _dt(gu), _stream())
+def silu_mul(gu, out, bias=None):
+    """out[m, f] = silu(gu[m, f] + b[f]) * (gu[m, F + f] + b[F + f]); bias float32 [2F] or None."""
+    _req(gu, gu.dtype), _req(out, gu.dtype), _f32(bias)
+    _call("dli_silu_mul", 1, _p(gu), _p(out), gu.shape[0], out.shape[1], gu.shape[1], _dt(gu), _p(bias), _stream())
     return out
 
 
 def attn_prep_append(proj, qbuf, k_cache, v_cache, row_ent, ent, page_table, H, G, D, V, rd, q_off, k_off, v_off,
-                     q_norm, k_norm, eps, cos_qk, sin_qk, cos_v, sin_v):
-    """q/k head norms, rotation and value rotation of a ragged step; q -> qbuf (float32), k / v -> the paged caches."""
+                     q_norm, k_norm, eps, cos_qk, sin_qk, cos_v, sin_v, bias=None, q_only=False):
+    """q/k head norms, rotation and value rotation of a ragged step; q -> qbuf (float32), k / v -> the paged caches.
+    bias float32 (indexed like proj's columns) is added first; q_only: no keys or values are made or appended (the caches
+    are only asked for their page size)."""
     _req(proj, proj.dtype), _req(k_cache, proj.dtype), _req(v_cache, proj.dtype)
-    _f32(qbuf, q_norm, k_norm, cos_qk, sin_qk, cos_v, sin_v), _i32(row_ent, ent, page_table)
+    _f32(qbuf, q_norm, k_norm, cos_qk, sin_qk, cos_v, sin_v, bias), _i32(row_ent, ent, page_table)
     tl = cos_qk.shape[0] if cos_qk is not None else (cos_v.shape[0] if cos_v is not None else 0)
     _call("dli_attn_prep_append", 1, _p(proj), _p(qbuf), _p(k_cache), _p(v_cache), _p(row_ent), _p(ent), _p(page_table),
           page_table.shape[1], k_cache.shape[2], proj.shape[0], H, G, D, V, rd, proj.shape[1], q_off, k_off, v_off,
-          _p(q_norm), _p(k_norm), float(eps), _p(cos_qk), _p(sin_qk), _p(cos_v), _p(sin_v), tl, _dt(proj), _stream())
+          _p(q_norm), _p(k_norm), float(eps), _p(cos_qk), _p(sin_qk), _p(cos_v), _p(sin_v), tl, _dt(proj), _p(bias),
+          1 if q_only else 0, _stream())
 
 
 def attn_ragged(qbuf, k_cache, v_cache, proj, out, row_ent, ent, page_table, H, G, D, V, scale, chunk=0, window=0,
-                sink=None, g_off=-1, cos_v=None, sin_v=None, ldv=0, splits=1, part=None, first=0):
+                sink=None, g_off=-1, cos_v=None, sin_v=None, ldv=0, splits=1, part=None, first=0, r1=None, r2=None):
     """Chunk- / window-masked attention with an optional sink and output gate over the paged cache -> out [rows, H*V].
+    r1, r2 float32 [H]: the distance penalty r1 ln(1 + r2 (i - j)) on the scaled scores.
     first: positions below it stay visible whatever the chunk or window says.
     ldv: elements between value rows (0 = V); v_cache may be k_cache itself (values = leading part of the keys).
     splits > 1: every row's keys are dealt to that many CTAs; part: float32 scratch of rows * H * splits * (V + 2)."""
-    _f32(qbuf, sink, cos_v, sin_v, part), _i32(row_ent, ent, page_table), _req(out, k_cache.dtype), _req(proj, k_cache.dtype)
+    _f32(qbuf, sink, cos_v, sin_v, part, r1, r2), _i32(row_ent, ent, page_table), _req(out, k_cache.dtype), _req(proj, k_cache.dtype)
     if splits > 1 and part.numel() < qbuf.shape[0] * H * splits * (V + 2):
         raise ValueError("attn_ragged: scratch too small for the key splits")
     _call("dli_attn_ragged", 2 if splits > 1 else 1, _p(qbuf), _p(k_cache), _p(v_cache), _p(proj), _p(out), _p(row_ent), _p(ent),
           _p(page_table), page_table.shape[1], k_cache.shape[2], qbuf.shape[0], H, G, D, V, float(scale), int(chunk),
           int(window), int(first), _p(sink), proj.shape[1] if proj is not None else 0, g_off, _p(cos_v), _p(sin_v), int(ldv),
-          int(splits), _p(part), _dt(k_cache), _stream())
+          int(splits), _p(part), _dt(k_cache), _p(r1), _p(r2), _stream())
     return out
 
 
@@ -611,16 +618,17 @@ def attn_ragged_tc_supported(D, V, dtype) -> bool:
 
 
 def attn_ragged_tc(qbuf, k_cache, v_cache, proj, out, ent, tiles, page_table, H, G, D, V, scale, chunk=0, window=0,
-                   sink=None, g_off=-1, cos_v=None, sin_v=None, page_base=0, first=0):
+                   sink=None, g_off=-1, cos_v=None, sin_v=None, page_base=0, first=0, r1=None, r2=None):
     """attn_ragged for steps with portions of prompts, on the tensor cores: tiles int32 [n_tiles, 2] = (entry, first
     row of the 64-row query tile within the entry).  page_base: k_cache / v_cache hold pages page_base.. of the pool only
     (the pages the step's sequences use must all lie in that range)."""
-    _f32(qbuf, sink, cos_v, sin_v), _i32(ent, tiles, page_table), _req(out), _req(proj), _req(k_cache), _req(v_cache)
+    _f32(qbuf, sink, cos_v, sin_v, r1, r2), _i32(ent, tiles, page_table), _req(out), _req(proj), _req(k_cache), _req(v_cache)
     kb = page_base * k_cache.stride(0) * k_cache.element_size()
     vb = page_base * v_cache.stride(0) * v_cache.element_size()
     _call("dli_attn_ragged_tc", 1, _p(qbuf), _p(k_cache) - kb, _p(v_cache) - vb, _p(proj), _p(out), _p(ent), _p(tiles),
           tiles.numel() // 2, _p(page_table), page_table.shape[1], k_cache.shape[2], H, G, D, V, float(scale), int(chunk),
-          int(window), int(first), _p(sink), proj.shape[1] if proj is not None else 0, g_off, _p(cos_v), _p(sin_v), _stream())
+          int(window), int(first), _p(sink), proj.shape[1] if proj is not None else 0, g_off, _p(cos_v), _p(sin_v), _p(r1),
+          _p(r2), _stream())
     return out
 
 
@@ -752,19 +760,22 @@ def gated_group_rmsnorm(y, proj, w, out, groups, eps, z_off):
     return out
 
 
-def moe_route(h, w_router, correction, wts, idw, sel_idx, sel_w, n_real, top):
+def moe_route(h, w_router, correction, wts, idw, sel_idx, sel_w, n_real, top, groups=1, keep=1, wscale=1.0, renorm=True):
     """Router of a mixture of experts on float32 rows: dense weights wts [rows, n_real], pass-through weight idw [rows],
-    the choice sel_idx / sel_w [rows, top]."""
+    the choice sel_idx / sel_w [rows, top].  groups > 1: only outputs of the `keep` best of that many equal groups can be
+    chosen; renorm False: the weights are the scores themselves; both times wscale."""
     _f32(h, w_router, correction, wts, idw, sel_w), _i32(sel_idx)
     _call("dli_moe_route", 1, _p(h), _p(w_router), _p(correction), _p(wts), _p(idw), _p(sel_idx), _p(sel_w), h.shape[0],
-          h.shape[1], w_router.shape[0], int(n_real), int(top), _stream())
+          h.shape[1], w_router.shape[0], int(n_real), int(top), int(groups), int(keep), float(wscale), 1 if renorm else 0,
+          _stream())
 
 
-def moe_act(gu, wts, act, n_exp, ff, limit, ff_s=0, limit_s=0.0, alpha=1.702):
-    """Clamped gated activation of all experts' stacked gate/up rows, times the routing weights."""
+def moe_act(gu, wts, act, n_exp, ff, limit, ff_s=0, limit_s=0.0, alpha=1.702, gated=True):
+    """Activation of all experts' stacked projections, times the routing weights: the clamped gated form on [gate; up] rows,
+    or (gated False) max(u, 0)^2 on up rows alone."""
     _req(gu, gu.dtype), _req(act, gu.dtype), _f32(wts)
     _call("dli_moe_act", 1, _p(gu), _p(wts), _p(act), gu.shape[0], int(n_exp), int(ff), float(limit), int(ff_s),
-          float(limit_s), float(alpha), gu.shape[1], _dt(gu), _stream())
+          float(limit_s), float(alpha), gu.shape[1], _dt(gu), 0 if gated else 1, _stream())
     return act
 
 
@@ -772,12 +783,43 @@ def moe_sel_supported(d, ff, ff_s, top) -> bool:
     return bool(_lib.load().dli_moe_sel_supported(int(d), int(ff), int(ff_s), int(top)))
 
 
-def moe_sel(x, w_gu, w_down, sel_idx, sel_w, act_sel, y, n_exp, top, ff, limit, ff_s=0, limit_s=0.0, alpha=1.702):
+def moe_sel(x, w_gu, w_down, sel_idx, sel_w, act_sel, y, n_exp, top, ff, limit, ff_s=0, limit_s=0.0, alpha=1.702, gated=True):
     """Few rows (decode): the chosen experts' and the shared expert's weights only -> y [rows, d] (bf16)."""
     _req(x), _req(w_gu), _req(w_down), _req(act_sel), _req(y), _i32(sel_idx), _f32(sel_w)
     _call("dli_moe_sel_bf16", 2, _p(x), _p(w_gu), _p(w_down), _p(sel_idx), _p(sel_w), _p(act_sel), _p(y), x.shape[0],
-          x.shape[1], int(n_exp), int(top), int(ff), float(limit), int(ff_s), float(limit_s), float(alpha), _stream())
+          x.shape[1], int(n_exp), int(top), int(ff), float(limit), int(ff_s), float(limit_s), float(alpha), 0 if gated else 1,
+          _stream())
     return y
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Pre-norm layers with layer scale, token shift and depth average (prenorm_rows.cu)
+def layer_close(x, y=None, bias=None, idw=None, h_in=None, ls=None, xs=None, n_prev=0, dwa=None, w_next=None, shift=None,
+                tail=None, ent=None, out_f=None, out_e=None, eps: float = 1e-6):
+    """x += ls * (y + bias + idw[:, None] * h_in) (x float32 in place; y in the element type); with dwa (float32 [n_prev + 1])
+    the result is stored as xs[n_prev] and x becomes sum_j dwa[j] * xs[j] (xs float32 [n, rows_cap, d]); with w_next the
+    normed x goes to out_f (float32) / out_e (element type); shift (steps of one row per entry): the normed row is mixed
+    with the slot's stored row (tail float32 [slots, d]), which it replaces."""
+    _f32(x, bias, idw, h_in, ls, xs, dwa, w_next, shift, tail, out_f), _i32(ent)
+    for t in (y, out_e):
+        if t is not None:
+            _req(t, t.dtype)
+    ref = y if y is not None else out_e
+    if dwa is not None and (xs is None or xs.shape[0] <= n_prev or dwa.numel() < n_prev + 1):
+        raise ValueError("layer_close: the depth average needs n_prev + 1 weights and stored results")
+    _call("dli_layer_close", 1, _p(y), _p(bias), _p(idw), _p(h_in), _p(ls), _p(x), _p(xs), xs.stride(0) if xs is not None else 0,
+          int(n_prev), _p(dwa), _p(w_next), _p(shift), _p(tail), _p(ent), _p(out_f), _p(out_e), x.shape[0], x.shape[1],
+          float(eps), _dt(ref) if ref is not None else 1, _stream())
+    return x
+
+
+def token_shift_ragged(h, shift, tail, row_ent, ent, out):
+    """out = h + (previous row - h) * shift per channel; h float32 [rows, d] normed rows; an entry's first row takes the
+    slot's stored row (zeros at position 0) and stores the entry's last row in its place."""
+    _f32(h, shift, tail), _i32(row_ent, ent), _req(out, out.dtype)
+    _call("dli_token_shift_ragged", 1, _p(h), _p(shift), _p(tail), _p(row_ent), _p(ent), _p(out), h.shape[0], h.shape[1],
+          _dt(out), _stream())
+    return out
 
 
 # ---------------------------------------------------------------------------------------------------------------

@@ -3,10 +3,12 @@
 ShardEngine (engine.py) serves uniform Llama / GPT-2 stacks on rectangular batches with a bf16 residual stream.
 This engine serves stacks described layer by layer (HybridSpec): every layer has a token mixer — softmax attention
 with its options, latent attention, or a recurrent cell with a matrix state (mLSTM, state-space, gated delta rule) —
-and optionally a feed-forward (dense or a mixture of experts).  Three layer styles: sublayers in sequence, each
+and optionally a feed-forward (dense or a mixture of experts).  Four layer styles: sublayers in sequence, each
 wrapped in a pre-norm and a post-norm with one weight and reading its input through a short causal convolution;
 mixer and feed-forward side by side on one grouped norm; sublayers that read the residual stream itself and are
-normed on their output only, followed by a per-layer token input.  Layers may share another layer's weights while
+normed on their output only, followed by a per-layer token input; pre-normed sublayers with a weight vector per
+norm, a layer scale on each result, a token shift in front of the mixer and an average over all layers' results
+after the layer.  Layers may share another layer's weights while
 keeping a cache / state of their own, or read another layer's cache.  The residual stream, norms, rotation
 angles, scores, softmax weights, convolution and recurrent state are fp32; projections run in the element type of the
 engine (bf16 on the tcgen05 / GEMV kernels of ops.linear, or float32 on the CUDA-core GEMM).
@@ -62,6 +64,8 @@ class MixerSpec:
     out_gate: bool = False         # sigmoid gate per output channel (head_gate: one per head)
     rot_halves: bool = False       # rotation pairs (i, i + rot_dims/2) instead of interleaved (2i, 2i+1)
     kv_from: Optional[int] = None  # the layer reads that (earlier) layer's cache and writes none of its own
+    bias: bool = False             # attention: q / k / v projections have biases
+    dist_penalty: bool = False     # attention: r1[h] ln(1 + r2[h] (i - j)) is taken off the scaled scores
     # mamba2: state rows per head, B/C groups, groups of the gated output norm, taps of the x/B/C convolution
     state: int = 0
     groups: int = 1
@@ -84,6 +88,11 @@ class MoESpec:
     shared_ff: int = 0
     shared_limit: float = 0.0
     alpha: float = 1.702           # g * sigmoid(alpha * g)
+    gated: bool = True             # False: experts are down(max(up x, 0)^2), no gate, no clamps
+    groups: int = 1                # > 1: router outputs form that many equal groups; only the `keep` best groups' outputs
+    keep: int = 1                  # can be chosen
+    route_scale: float = 1.0       # factor on the routing weights
+    renorm: bool = True            # weights divided by the sum of the chosen scores (False: the scores themselves)
 
     @property
     def total_ff(self) -> int:
@@ -106,6 +115,11 @@ class LayerSpec:
     ff_alpha: float = 1.702
     side_dim: int = 0              # > 0: after the feed-forward, the per-layer token input of this size ...
     side_off: int = 0              # ... read at this column of the side embedding table
+    pre_norm: bool = False         # True: x += ls1 * mixer(norm1(x)); x += ls2 * ff(norm2(x)) with weight vectors, and:
+    token_shift: bool = False      # the mixer reads h_t + (h_(t-1) - h_t) * shift of its normed input (a row per slot)
+    layer_scale: bool = False      # vectors ls1 / ls2 on the sublayers' results
+    depth_avg: bool = False        # after the layer x <- sum_j dwa[j] X_j over the embedding output and all results so far
+    ff_bias: bool = False          # the dense feed-forward's projections have biases
 
 
 @dataclass
@@ -120,6 +134,8 @@ class HybridSpec:
     norm_groups: int = 0           # > 0: the final norm (and the norm of parallel layers) is grouped with a weight vector
     loop_passes: int = 0           # > 0: the model has the loop re-entry projection and per-pass vectors
     side_width: int = 0            # > 0: columns of the side embedding table [vocab, side_width]
+    pos_sinusoid: bool = False     # the embedding output gets sin / cos (position * pos_base^(-2i/width)) added
+    pos_base: float = 10000.0
 
     @property
     def n_layers(self) -> int:
@@ -181,10 +197,12 @@ class RaggedEngine:
                 self.kv_index[i] = self.kv_index[L.mixer.kv_from]
         self.slots = StateSlots(self.max_batch, self.device)
         for i, L in enumerate(spec.layers):
-            if spec.taps > 1 and not L.post_only:
+            if spec.taps > 1 and not L.post_only and not L.pre_norm:
                 self.slots.add(("tail1", i), spec.taps - 1, spec.width)
                 if L.ff:
                     self.slots.add(("tail2", i), spec.taps - 1, spec.width)
+            if L.pre_norm and L.token_shift:
+                self.slots.add(("shift", i), spec.width)  # the previous position's normed mixer input
             if L.mixer.kind == "delta":
                 m = L.mixer
                 self.slots.add(("S", i), m.heads, m.vdim, m.dim)  # value-major: the transposed state
@@ -264,23 +282,38 @@ class RaggedEngine:
         if s.loop_passes:
             self.w["loop_in"] = mat(t["loop_in"], pad_rows=False)
             self.w["loop_step"] = f32(t["loop_step"])
+        if s.pos_sinusoid:
+            # frequencies in float64 on the host, rounded once; the angle position * frequency is formed in fp32
+            self.w["pos_freq"] = torch.tensor([s.pos_base ** (-2.0 * i / s.width) for i in range((s.width + 1) // 2)],
+                                              dtype=torch.float64).to(torch.float32).to(dev)
         self.layers = {}
         for i, src in t["layers"].items():
             L, m = s.layers[i], s.layers[i].mixer
-            d = {} if L.post_only else {"canon1": f32(src["canon1"])}
-            if L.parallel or L.post_only:
+            d = {} if (L.post_only or L.pre_norm) else {"canon1": f32(src["canon1"])}
+            if L.parallel or L.post_only or L.pre_norm:
                 d["norm1"] = vec(src["norm1"])
             else:
                 d["norm1"], d["norm1b"] = float(src["norm1"]), float(src["norm1b"])
             qn, kn, vn = m.heads * m.dim, m.kv_heads * m.dim, m.kv_heads * m.vdim
-            if m.kind == "attention":
+            if m.kind == "attention" and m.kv_from is not None:
+                # only queries: keys and values are the source layer's cache
+                if m.head_gate or m.qk_norm or m.rot_dims or m.rotate_values:
+                    raise ValueError(f"layer {i}: another layer's cache with a gate, head norms or rotation is not supported")
+                d["w_proj"] = mat(src["q"])
+                d["off"] = {"q": 0, "k": 0, "v": 0, "g": -1}
+                d["q_norm"] = d["k_norm"] = d["sink"] = None
+                d["qkv_b"] = vec(src["q_b"]) if m.bias else None
+                d["r1"], d["r2"] = (vec(src["r1"]), vec(src["r2"])) if m.dist_penalty else (None, None)
+            elif m.kind == "attention":
                 d["w_proj"] = mat(src["q"], src["k"], src["v"], src["g"]) if m.head_gate else mat(src["q"], src["k"], src["v"])
                 d["off"] = {"q": 0, "k": qn, "v": qn + kn, "g": qn + kn + vn if m.head_gate else -1}
+                d["qkv_b"] = vec(torch.cat([src[k].reshape(-1).float() for k in ("q_b", "k_b", "v_b")])) if m.bias else None
                 # a norm without weights is the norm with unit weights
                 ones = torch.ones(m.dim, dtype=torch.float32, device=dev)
                 d["q_norm"] = (vec(src["q_norm"]) if "q_norm" in src else ones) if m.qk_norm else None
                 d["k_norm"] = (vec(src["k_norm"]) if "k_norm" in src else ones) if m.qk_norm else None
                 d["sink"] = vec(src["sink"]) if m.sink else None
+                d["r1"], d["r2"] = (vec(src["r1"]), vec(src["r2"])) if m.dist_penalty else (None, None)
             elif m.kind == "mlstm":
                 gn = m.heads * m.vdim
                 d["w_proj"] = mat(src["q"], src["k"], src["v"], src["g"], src["i"], src["f"])
@@ -329,7 +362,25 @@ class RaggedEngine:
             if L.side_dim:
                 d["side_gate"], d["side_proj"] = mat(src["side_gate"], pad_rows=False), mat(src["side_proj"], pad_rows=False)
                 d["side_norm"] = vec(src["side_norm"])
-            if L.ff and L.post_only:
+            if L.pre_norm:
+                for k in ("shift", "ls1", "ls2", "dwa"):
+                    d[k] = vec(src[k]) if k in src else None
+                if d["dwa"] is not None and d["dwa"].numel() != i + 2:
+                    raise ValueError(f"layer {i}: {d['dwa'].numel()} averaging weights for {i + 2} results")
+                if L.ff or L.moe is not None:
+                    d["norm2"] = vec(src["norm2"])
+            if L.ff and L.pre_norm:
+                # silu(gate) * up as the GEMM's epilogue where there are no biases and the tile's alignment holds; else
+                # [gate rows | up rows] and the activation (with the biases) as a kernel of its own
+                d["packed"] = E == BF and not L.ff_bias and L.ff % 128 == 0 and s.width % 8 == 0
+                if d["packed"]:
+                    d["w_gu"] = ops.pack_gate_up(src["gate"].to(BF), src["up"].to(BF)).to(dev)
+                else:
+                    d["w_gu"] = mat(src["gate"], src["up"], pad_rows=False)
+                d["gu_b"] = vec(torch.cat((src["gate_b"].reshape(-1).float(), src["up_b"].reshape(-1).float()))) if L.ff_bias else None
+                d["down_b"] = vec(src["down_b"]) if L.ff_bias else None
+                d["w_down"] = mat(src["down"], pad_rows=False)
+            elif L.ff and L.post_only:
                 d["norm2"] = vec(src["norm2"])
                 # the tensor-core path interleaves gate and up rows so that the clamped activation is the GEMM's epilogue;
                 # other shapes: [gate rows | up rows] and the activation as a kernel of its own
@@ -354,10 +405,10 @@ class RaggedEngine:
                 # all experts as ONE gate/up matrix (per expert [gate; up], the shared expert last) and ONE down matrix
                 # over the concatenated expert activations: the routing weights are applied between the two
                 e = L.moe
-                blocks = [x for g_, u_, _ in src["experts"] for x in (g_, u_)]
+                blocks = [x for g_, u_, _ in src["experts"] for x in ((g_, u_) if e.gated else (u_,))]
                 downs = [d_ for _, _, d_ in src["experts"]]
                 if e.shared_ff:
-                    blocks += [src["shared"][0], src["shared"][1]]
+                    blocks += [src["shared"][0], src["shared"][1]] if e.gated else [src["shared"][1]]
                     downs.append(src["shared"][2])
                 d["w_gu"] = mat(*blocks)
                 d["w_down"] = torch.cat([x.to(E) for x in downs], dim=1).contiguous().to(dev)
@@ -441,9 +492,14 @@ class RaggedEngine:
         if sides:
             self._sg = torch.empty(rows * max(sides), dtype=E, device=dev)
             self._sa = torch.empty(rows * max(sides), dtype=E, device=dev)
-        if any(L.parallel for L in s.layers):
+        if any(L.parallel or L.pre_norm for L in s.layers):
             self._he = torch.empty(rows, s.width, dtype=E, device=dev)
             self._y2 = torch.empty(rows, s.width, dtype=E, device=dev)
+        if any(L.pre_norm and L.token_shift for L in s.layers):
+            self._hs = torch.empty(rows, s.width, dtype=f32, device=dev)  # normed rows before the token shift
+        if any(L.pre_norm and L.depth_avg for L in s.layers):
+            # the embedding output and every layer's result, for the averages after the layers
+            self._xs = torch.empty(s.n_layers + 1, rows, s.width, dtype=f32, device=dev)
         moes = [L.moe for L in s.layers if L.moe is not None]
         if moes:
             self._wts = torch.empty(rows * max(e.experts for e in moes), dtype=f32, device=dev)
@@ -614,11 +670,33 @@ class RaggedEngine:
         x0 = self._x0[:rows] if s.loop_passes else None
         # a first layer that reads the residual stream itself gets its GEMM operand from the same kernel
         first_post = s.layers and s.layers[0].post_only and E != torch.float32
-        ops.embedding_f32(d_tok, self.w["embed"], x, s.embed_scale, out2=x0, out_e=hc if first_post else None)
+        if x0 is None and any(L.pre_norm and L.depth_avg for L in s.layers):
+            x0 = self._xs[0][:rows]
+        ops.embedding_f32(d_tok, self.w["embed"], x, s.embed_scale, out2=x0, out_e=hc if first_post else None,
+                          row_ent=d_rent if s.pos_sinusoid else None, ent=d_ent if s.pos_sinusoid else None,
+                          inv_freq=self.w["pos_freq"] if s.pos_sinusoid else None)
         pt = self.kv.page_table
         y_prev, g_prev = None, 1.0
+        opened = final_done = False  # pre-norm layers: the previous layer's last kernel already made this one's input / the final norm
         for li, L in enumerate(s.layers):
             P, m = self.layers[s.source(li)], L.mixer
+            if L.pre_norm:
+                if y_prev is not None:  # close the sequential sublayer before it
+                    ops.postnorm_add_norm(y_prev, x, g_prev, s.eps)
+                    y_prev = None
+                nxt = s.layers[li + 1] if li + 1 < s.n_layers else None
+                if nxt is None:
+                    follow = ("final", self.w["final_norm"], None, None) if (s.norm_groups == 1 and nw) else (None, None, None, None)
+                elif nxt.pre_norm:
+                    Pn = self.layers[s.source(li + 1)]
+                    follow = ("layer", Pn["norm1"], Pn["shift"], self.slots.tensors.get(("shift", li + 1)))
+                else:
+                    follow = (None, None, None, None)
+                self._pre_norm_layer(li, L, P, rows, n_ent, views, tiles, opened, follow)
+                opened, final_done = follow[0] == "layer", follow[0] == "final"
+                if self.layer_trace is not None:
+                    self.layer_trace.append(x.clone())
+                continue
             if L.reenter is not None or L.parallel:
                 if y_prev is not None:  # close the sequential sublayer before it
                     ops.postnorm_add_norm(y_prev, x, g_prev, s.eps)
@@ -691,7 +769,7 @@ class RaggedEngine:
         if s.norm_groups:
             if y_prev is not None:
                 ops.postnorm_add_norm(y_prev, x, g_prev, s.eps)
-            if nw:
+            if nw and not final_done:
                 ops.group_rmsnorm(x, self.w["final_norm"], s.norm_groups, s.eps, hn=hn)
         elif y_prev is None:
             ops.scalar_rmsnorm(x, self.w["final_norm"], s.eps, hn)
@@ -773,6 +851,92 @@ class RaggedEngine:
                 self._lin(sa, P["side_proj"], y)
                 ops.postnorm_vec_add(y, x, P["side_norm"], s.eps, he=he)
 
+    # ------------------------------------------------------------------ pre-norm layers with layer scale, shift and average
+    def _pre_norm_layer(self, li, L, P, rows, n_ent, views, tiles, opened, follow):
+        """x += ls1 * mixer(shift(norm1(x))); x += ls2 * ff(norm2(x)); X_(li+1) = x; x = sum_j dwa[j] X_j.
+        Everything between two projections is ONE kernel (ops.layer_close): the scaled residual add, the average and the
+        norm that follows — the feed-forward's, the next layer's (follow = ("layer", weights, shift, slot rows)) or the
+        model's last one (("final", weights, ..)).  opened: the previous layer's closing kernel already wrote this mixer's
+        input.  Steps of one row per entry (decode) also get the next mixer's token shift from that kernel; steps with
+        portions of prompts shift the normed rows in a kernel of their own, which needs the previous ROW."""
+        s, E = self.spec, self.dtype
+        d_tok, d_rent, d_ent, d_want, d_tiles = views
+        x, hn, hc, he, y = self._x[:rows], self._hn[:rows], self._hc[:rows], self._he[:rows], self._y[:rows]
+        single = rows == n_ent
+        m = L.mixer
+
+        def open_mixer(Pm, tail, y_=None, **close):
+            """Closing kernel (if any work is left for it) + the norm in front of a mixer + its token shift -> hc."""
+            if Pm["shift"] is None:
+                ops.layer_close(x, y_, w_next=Pm["norm1"], out_e=hc, eps=s.eps, **close)
+            elif single:
+                ops.layer_close(x, y_, w_next=Pm["norm1"], shift=Pm["shift"], tail=tail, ent=d_ent, out_e=hc, eps=s.eps, **close)
+            else:
+                hs = self._hs[:rows]
+                ops.layer_close(x, y_, w_next=Pm["norm1"], out_f=hs, eps=s.eps, **close)
+                ops.token_shift_ragged(hs, Pm["shift"], tail, d_rent, d_ent, hc)
+
+        if not opened:
+            open_mixer(P, self.slots.tensors.get(("shift", li)))
+        n_proj = P["w_proj"].shape[0]
+        proj = self._proj[:rows * n_proj].view(rows, n_proj)
+        self._lin(hc, P["w_proj"], proj)
+        n_mix = m.heads * m.vdim
+        mix = self._mix[:rows * n_mix].view(rows, n_mix)
+        if m.kind != "attention":
+            raise ValueError(f"layer {li}: mixer {m.kind!r} has no pre-norm form")
+        self._attention(li, m, P, proj, mix, rows, views, tiles)
+        self._lin(mix, P["wo"], y)
+        close = {"ls": P["ls1"]}
+        y_last = y
+        if L.ff:
+            ops.layer_close(x, y, ls=P["ls1"], w_next=P["norm2"], out_e=he, eps=s.eps)
+            act = self._act[:rows * L.ff].view(rows, L.ff)
+            if P["packed"] and 2 < rows <= 128 and s.width % 64 == 0:
+                ops.linear_splitk_gated_silu(he, P["w_gu"], self._splitk(), out=act)
+            elif P["packed"]:
+                ops.linear_gated_silu(he, P["w_gu"], out=act)
+            else:
+                gu = self._gu[:rows * 2 * L.ff].view(rows, 2 * L.ff)
+                self._lin(he, P["w_gu"], gu)
+                ops.silu_mul(gu, act, bias=P["gu_b"])
+            self._lin(act, P["w_down"], y)
+            close = {"ls": P["ls2"], "bias": P["down_b"]}
+        elif L.moe is not None:
+            e = L.moe
+            ops.layer_close(x, y, ls=P["ls1"], w_next=P["norm2"], out_f=hn, out_e=he, eps=s.eps)
+            y_last = self._y2[:rows]
+            wts = self._wts[:rows * e.experts].view(rows, e.experts)
+            idw = self._idw[:rows]
+            sel_idx, sel_w = self._sel_idx[:rows * e.top].view(rows, e.top), self._sel_w[:rows * e.top].view(rows, e.top)
+            ops.moe_route(hn, P["w_router"], P["corr"], wts, idw, sel_idx, sel_w, e.experts, e.top, groups=e.groups,
+                          keep=e.keep, wscale=e.route_scale, renorm=e.renorm)
+            if E == BF and rows <= self.moe_sel_max_rows and self.moe_sel_share * (e.top * e.ff + e.shared_ff) <= e.total_ff and \
+                    ops.moe_sel_supported(s.width, e.ff, e.shared_ff, e.top):
+                # decode rows of a sparse enough mixture: stream only the chosen experts' weights
+                n_sel = e.top * e.ff + e.shared_ff
+                ops.moe_sel(he, P["w_gu"], P["w_down"], sel_idx, sel_w, self._act[:rows * n_sel].view(rows, n_sel), y_last,
+                            e.experts, e.top, e.ff, e.limit, e.shared_ff, e.shared_limit, e.alpha, gated=e.gated)
+            else:
+                n_gu = P["w_gu"].shape[0]
+                gu = self._gu[:rows * n_gu].view(rows, n_gu)
+                self._lin(he, P["w_gu"], gu)
+                act = self._act[:rows * e.total_ff].view(rows, e.total_ff)
+                ops.moe_act(gu, wts, act, e.experts, e.ff, e.limit, e.shared_ff, e.shared_limit, e.alpha, gated=e.gated)
+                self._lin(act, P["w_down"], y_last)
+            close = {"ls": P["ls2"]}
+            if e.identity:
+                close.update(idw=idw, h_in=hn)
+        if P["dwa"] is not None:
+            close.update(xs=self._xs, n_prev=li + 1, dwa=P["dwa"])
+        kind, w_next, shift_next, tail_next = follow
+        if kind == "layer":
+            open_mixer({"norm1": w_next, "shift": shift_next}, tail_next, y_last, **close)
+        elif kind == "final":
+            ops.layer_close(x, y_last, w_next=w_next, out_f=hn, eps=s.eps, **close)
+        else:
+            ops.layer_close(x, y_last, eps=s.eps, **close)
+
     def _attention(self, li, m, P, proj, mix, rows, views, tiles):
         """Softmax attention over the layer's paged keys and values: prep (head norms, rotation, append), then the
         tensor-core tiles for steps with portions of prompts where the sizes have one, else the row-wise kernel."""
@@ -783,20 +947,26 @@ class RaggedEngine:
         cq, sq = self._table(m.rot_base, m.rot_dims, m.rot_scaling) if m.rot_dims else (None, None)
         cv, sv = self._table(m.rot_base, m.vdim, None) if m.rotate_values else (None, None)
         qbuf = self._qbuf[:rows * m.heads * m.dim].view(rows, m.heads * m.dim)
+        r1, r2 = P.get("r1"), P.get("r2")
         ops.attn_prep_append(proj, qbuf, kc, vc, d_rent, d_ent, pt, m.heads, m.kv_heads, m.dim, m.vdim,
                              m.rot_dims, off["q"], off["k"], off["v"], P["q_norm"], P["k_norm"], s.eps,
-                             cq, sq, cv, sv)
+                             cq, sq, cv, sv, bias=P.get("qkv_b"), q_only=m.kv_from is not None)
         if tiles and m.scale > 0 and ops.attn_ragged_tc_supported(m.dim, m.vdim, E):
             ops.attn_ragged_tc(qbuf, kc, vc, proj, mix, d_ent, d_tiles, pt, m.heads, m.kv_heads, m.dim, m.vdim,
                                m.scale, chunk=m.chunk, window=m.window, sink=P["sink"], g_off=off["g"],
-                               cos_v=cv, sin_v=sv, first=m.keep_first)
+                               cos_v=cv, sin_v=sv, first=m.keep_first, r1=r1, r2=r2)
         else:
             # few rows (decode): every row's keys go to several CTAs, so that a long context is read by many SMs; the
-            # count depends on the rows alone (a replayed graph keeps it while the contexts grow)
+            # count depends on the rows alone (a replayed graph keeps it while the contexts grow).  A row never sees more
+            # keys than its block or window (plus the kept first positions): no more splits than 32-key pieces of that
             splits = max(1, min(16, (4 * self._sms) // (rows * m.heads))) if rows <= 16 else 1
+            span = min([v for v in (m.chunk, m.window) if v > 0] or [0])
+            if span:
+                splits = max(1, min(splits, (span + m.keep_first + 31) // 32))
             ops.attn_ragged(qbuf, kc, vc, proj, mix, d_rent, d_ent, pt, m.heads, m.kv_heads, m.dim, m.vdim,
                             m.scale, chunk=m.chunk, window=m.window, sink=P["sink"], g_off=off["g"], cos_v=cv,
-                            sin_v=sv, first=m.keep_first, splits=splits, part=self._apart_att if splits > 1 else None)
+                            sin_v=sv, first=m.keep_first, splits=splits, part=self._apart_att if splits > 1 else None,
+                            r1=r1, r2=r2)
 
     def _delta(self, li, m, P, proj, mix, rows, views, long_step=False):
         """Gated delta rule: short convolutions and SiLU of q | k | v (fp32), the recurrence over the state slot, then

@@ -411,9 +411,12 @@ int dli_decode_advance(const int32_t* tokens, int32_t* token_log, int32_t* posit
  * every norm, convolution state, recurrent state, angle, score and softmax weight
  * is fp32 for both. */
 /* x = table[ids] * scale as fp32; x2 (optional) receives the same rows (a model that re-reads its embedding output),
- * xe (optional) the same rows in the element type (a first layer that reads the residual stream as a GEMM operand). */
+ * xe (optional) the same rows in the element type (a first layer that reads the residual stream as a GEMM operand).
+ * inv_freq [ceil(d/2)] fp32 (optional, with row_ent / ent): a sinusoidal position vector is added, channel 2i
+ * sin(p * inv_freq[i]) and channel 2i+1 the cosine, p the row's position in its sequence (fp32 angles). */
 int dli_embedding_f32(const int32_t* ids, const void* table, float* x, float* x2, void* xe, int rows, int d, int vocab,
-                      float scale, int dt, dli_stream_t stream);
+                      float scale, int dt, const int32_t* row_ent, const int32_t* ent, const float* inv_freq,
+                      dli_stream_t stream);
 /* RMS norm in `groups` equal consecutive parts of the row, each by its own root mean square, times w [d] fp32;
  * hn (fp32) and he (element type dt) are optional outputs. */
 int dli_group_rmsnorm(const float* x, const float* w, float* hn, void* he, int rows, int d, int groups, float eps, int dt,
@@ -448,8 +451,8 @@ int dli_gather_cast(const float* src, const int32_t* rows, void* out, int n, int
 /* y[M,N] = x[M,K] . w[N,K]^T on the CUDA cores with fp32 accumulation: any shape, both element types. */
 int dli_linear_any(const void* x, const void* w, void* y, int M, int N, int K, int ldx, int ldy, int dt,
                    dli_stream_t stream);
-/* act[m, f] = silu(gu[m, f]) * gu[m, F + f] */
-int dli_silu_mul(const void* gu, void* act, int M, int F, int ld, int dt, dli_stream_t stream);
+/* act[m, f] = silu(gu[m, f] + b[f]) * (gu[m, F + f] + b[F + f]); bias [2F] fp32 or NULL */
+int dli_silu_mul(const void* gu, void* act, int M, int F, int ld, int dt, const float* bias, dli_stream_t stream);
 
 /* Attention of a ragged step.  dli_attn_prep_append: per-head RMS norm of q and k (q_norm / k_norm [D] fp32 or NULL),
  * rotation of the first rd dims (interleaved pairs; cos_qk / sin_qk [table_len, rd/2] fp32), rotation of the values
@@ -461,16 +464,20 @@ int dli_silu_mul(const void* gu, void* act, int M, int F, int ld, int dt, dli_st
  * by sigmoid(proj[row, g_off + h]) (g_off < 0: no gate) -> out [rows, H, V].  ldv: elements between the value rows of
  * consecutive positions (0 = V); with v_cache == k_cache and ldv = D the values are the first V entries of the keys.
  * splits > 1 (few rows over long contexts): the keys of every row are dealt to `splits` CTAs whose partial sums go
- * through part [rows, H, splits, V + 2] fp32 and a merge kernel. */
+ * through part [rows, H, splits, V + 2] fp32 and a merge kernel.
+ * bias (dli_attn_prep_append, fp32, indexed like the columns of proj, or NULL) is added to the q / k / v columns first;
+ * q_only != 0: only the queries are made, the layer reads another layer's cached keys and values.  r1 / r2 [H] fp32 (or
+ * both NULL): the distance penalty r1[h] * ln(1 + r2[h] * (i - j)) is taken off the scaled score of query i, key j. */
 int dli_attn_prep_append(const void* proj, float* qbuf, void* k_cache, void* v_cache, const int32_t* row_ent,
                          const int32_t* ent, const int32_t* page_table, int max_pages, int page_size, int rows, int H,
                          int G, int D, int V, int rd, int ldp, int q_off, int k_off, int v_off, const float* q_norm,
                          const float* k_norm, float eps, const float* cos_qk, const float* sin_qk, const float* cos_v,
-                         const float* sin_v, int table_len, int dt, dli_stream_t stream);
+                         const float* sin_v, int table_len, int dt, const float* bias, int q_only, dli_stream_t stream);
 int dli_attn_ragged(const float* qbuf, const void* k_cache, const void* v_cache, const void* proj, void* out,
                     const int32_t* row_ent, const int32_t* ent, const int32_t* page_table, int max_pages, int page_size,
                     int rows, int H, int G, int D, int V, float scale, int chunk, int window, int first, const float* sink,
                     int ldp, int g_off, const float* cos_v, const float* sin_v, int ldv, int splits, float* part, int dt,
+                    const float* r1, const float* r2,
                     dli_stream_t stream);
 
 /* The same attention for steps that hold portions of prompts, on the tensor cores (bf16 caches only): one CTA per
@@ -480,7 +487,8 @@ int dli_attn_ragged_tc_supported(int D, int V, int dt);
 int dli_attn_ragged_tc(const float* qbuf, const void* k_cache, const void* v_cache, const void* proj, void* out,
                        const int32_t* ent, const int32_t* tiles, int n_tiles, const int32_t* page_table, int max_pages,
                        int page_size, int H, int G, int D, int V, float scale, int chunk, int window, int first,
-                       const float* sink, int ldp, int g_off, const float* cos_v, const float* sin_v, dli_stream_t stream);
+                       const float* sink, int ldp, int g_off, const float* cos_v, const float* sin_v, const float* r1,
+                       const float* r2, dli_stream_t stream);
 
 /* Matrix-memory recurrent layer (mLSTM, stabilised): q, k, v, gate pre-activations and the output gate are columns
  * of proj [rows, ldp]; state S [slots, H, D, V], n [slots, H, D], m [slots, H] fp32 is read and advanced (an entry
@@ -556,10 +564,15 @@ int dli_gated_group_rmsnorm(const float* y, const void* proj, const float* w, vo
  * weight of the chosen pass-through experts, sel_idx / sel_w [rows, top] the choice.  dli_moe_act: gu [rows, ld] =
  * per routed expert [gate ff | up ff], then the shared expert's [gate ff_s | up ff_s]; act [rows, n_exp*ff + ff_s] =
  * min(g, limit) * sigmoid(alpha * min(g, limit)) * (clamp(u, -limit, limit) + 1) * weight (shared: weight 1). */
+/* groups > 1: the n_out outputs form that many equal groups of neighbours, a group's score is its largest score +
+ * correction, and only outputs of the `keep` best groups can be chosen.  renorm 0: the weights are the scores
+ * themselves; both forms times wscale.  mode 1 (dli_moe_act, dli_moe_sel_bf16): experts without a gate,
+ * act = max(u, 0)^2 * weight on gu [rows, ld] = the experts' stacked up projections [ff each], then the shared one's. */
 int dli_moe_route(const float* h, const float* w_router, const float* correction, float* wts, float* idw, int32_t* sel_idx,
-                  float* sel_w, int rows, int d, int n_out, int n_real, int top, dli_stream_t stream);
+                  float* sel_w, int rows, int d, int n_out, int n_real, int top, int groups, int keep, float wscale,
+                  int renorm, dli_stream_t stream);
 int dli_moe_act(const void* gu, const float* wts, void* act, int rows, int n_exp, int ff, float limit, int ff_s,
-                float limit_s, float alpha, int ld, int dt, dli_stream_t stream);
+                float limit_s, float alpha, int ld, int dt, int mode, dli_stream_t stream);
 /* Few rows (decode steps, bf16): only the weights of each row's chosen experts (and the shared expert) are read.
  * x [rows, d]; w_gu and w_down in the stacked layout of dli_moe_act ([gate; up] per expert, shared last;
  * w_down [d, n_exp*ff + ff_s]); act_sel [rows, top*ff + ff_s] scratch; y [rows, d] = the weighted sum of the chosen
@@ -567,7 +580,22 @@ int dli_moe_act(const void* gu, const float* wts, void* act, int rows, int n_exp
 int dli_moe_sel_supported(int d, int ff, int ff_s, int top);
 int dli_moe_sel_bf16(const void* x, const void* w_gu, const void* w_down, const int32_t* sel_idx, const float* sel_w,
                      void* act_sel, void* y, int rows, int d, int n_exp, int top, int ff, float limit, int ff_s,
-                     float limit_s, float alpha, dli_stream_t stream);
+                     float limit_s, float alpha, int mode, dli_stream_t stream);
+
+/* Pre-norm layers with a weight vector per norm.  dli_layer_close, one pass over the rows between two projections:
+ *   v = x + ls * (y + bias + idw[row] * h_in)     (y == NULL: v = x; bias, idw / h_in, ls optional, fp32)
+ *   dwa != NULL: X_(n_prev) = v is stored at xs + n_prev * xs_stride and v = sum_(j <= n_prev) dwa[j] X_j (the average
+ *                over the embedding output and every layer's result so far)
+ *   x = v;  w_next != NULL: h = v / sqrt(mean(v^2) + eps) * w_next -> out_f (fp32) and / or out_e (element type)
+ *   shift != NULL (steps of ONE row per entry): h <- h + (t - h) * shift with t the slot's stored row (zeros at
+ *                position 0), and the slot's row becomes the unshifted h.  tail [slots, d].
+ * dli_token_shift_ragged: the same shift for any step, on normed rows h [rows, d] fp32 -> out (element type). */
+int dli_layer_close(const void* y, const float* bias, const float* idw, const float* h_in, const float* ls, float* x,
+                    float* xs, size_t xs_stride, int n_prev, const float* dwa, const float* w_next, const float* shift,
+                    float* tail, const int32_t* ent, float* out_f, void* out_e, int rows, int d, float eps, int dt,
+                    dli_stream_t stream);
+int dli_token_shift_ragged(const float* h, const float* shift, float* tail, const int32_t* row_ent, const int32_t* ent,
+                           void* out, int rows, int d, int dt, dli_stream_t stream);
 
 /* Layers whose sublayers read the residual stream itself and are normed on their OUTPUT only.
  * dli_postnorm_vec_add: x += y / sqrt(mean(y^2) + eps) * w with w [d] fp32 (y == NULL: x stays), he (optional,
