@@ -894,6 +894,182 @@ def fubepel_kernel_times(eng, spec, T, peaks):
     return res
 
 
+# ---------------------------------------------------------------------------------- Gimudra beside Togalorn and Sokevik
+def gimudra_config(width, heads, kv, hd, ff, layers, vocab, block=512):
+    """The Gimudra design at the sizes of a Llama layer: attention inside blocks of `block` positions with the Llama
+    layer's head counts and head size; layer 0 with the dense feed-forward and a cache of its own, layer 1 with a cache
+    of its own, the later layers on layer 1's cache; layers 1.. with a mixture of 14 squared-ReLU experts of size ff/4
+    plus 2 pass-through outputs in 4 groups of which 2 are kept, 4 outputs per token."""
+    mix = {"heads": heads, "kv_heads": kv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "mask": {"size": block}}
+    moe = {"kind": "moe", "expert": {"ff": ff // 4},
+           "router": {"experts": 14, "identity": 2, "top": 4, "scale": 1.5, "groups": {"count": 4, "keep": 2}}}
+    out = []
+    for i in range(layers):
+        out.append({"type": "attention", "mixer": dict(mix, kv_from=1) if i >= 2 else dict(mix),
+                    "mlp": {"kind": "dense", "ff": ff} if i == 0 else moe})
+    return {"architecture": "Gimudra", "vocab": vocab, "width": width, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+            "layers": out}
+
+
+def run_gimudra_compare(args, peaks):
+    """Prefill and decode throughput of the Gimudra design beside the framework's closest models on RaggedEngine — the
+    Togalorn design (mixture of experts with pass-through outputs, attention with a cache) and the Sokevik design (the
+    same attention kernels under a block mask, dense feed-forward) — at equal layer sizes and depth, random weights, plus
+    each kernel of the new mechanisms alone against its roofline.  One JSON line; the default workload of this file is
+    untouched."""
+    from dli_b200 import gimudra, sokevik, togalorn
+    from dli_b200.ragged_engine import RaggedEngine
+
+    T, K, W = args.ctx, args.steps, args.warmup
+    out = {"metric": "gimudra_vs_togalorn_sokevik", "unit": "tokens/s", "ctx": T, "steps": K, "warmup": W, "dtype": "bf16",
+           "data": "synthetic", "peaks": peaks, "sizes": {}}
+    names = args.hybrid_sizes.split(",")
+    if len(names) > 1:
+        import subprocess
+        for name in names:
+            cmd = [sys.executable, os.path.abspath(__file__), "--compare-gimudra", "--hybrid-sizes", name, "--steps", str(K),
+                   "--warmup", str(W), "--ctx", str(T), "--batch", str(args.batch), "--page-size", str(args.page_size)]
+            p = subprocess.run(cmd, capture_output=True, text=True, check=True)
+            out["sizes"].update(json.loads(p.stdout.strip().splitlines()[-1])["sizes"])
+        return out
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for name in names:
+        width, heads, kv, hd, ff, layers, vocab = HYBRID_SIZES[name]
+        mods = ((gimudra, gimudra_config(width, heads, kv, hd, ff, layers, vocab), "gimudra"),
+                (togalorn, togalorn_config(width, heads, kv, hd, ff, layers, vocab), "togalorn"),
+                (sokevik, hybrid_config(width, heads, kv, hd, ff, layers, vocab, chunk=512), "sokevik"))
+        res = {}
+        for mod, cfg, tag in mods:
+            spec = mod.spec_from_config(cfg)
+            eng = RaggedEngine(spec, max_batch=max(args.batch, 8), max_seq_len=T + K + W + 64, page_size=args.page_size)
+            eng.load_tensors(mod.model_tensors(spec, mod.random_state_dict(spec, seed=1, std=0.02, device="cuda")))
+            res.update(ragged_throughput(eng, vocab, T, K, W, args.batch, tag, flush))
+            res[f"{tag}_kernels"] = {"gimudra": gimudra_kernel_times, "togalorn": togalorn_kernel_times,
+                                     "sokevik": hybrid_kernel_times}[tag](eng, spec, T, peaks)
+            eng.unload()
+            del eng
+            torch.cuda.empty_cache()
+        out["sizes"][name] = res
+    return out
+
+
+def gimudra_kernel_times(eng, spec, T, peaks):
+    """Each kernel of the Gimudra mechanisms alone at the step sizes of the comparison: a T-token portion (prefill) and
+    one token after T (decode), against its algorithmic HBM bytes or FLOPs and the measured peaks."""
+    from dli_b200 import ops
+
+    dev, E, W = eng.device, eng.dtype, spec.width
+    li_d = next(i for i, L in enumerate(spec.layers) if L.ff)
+    li_m = next(i for i, L in enumerate(spec.layers) if L.moe is not None)
+    n_last = spec.n_layers
+    hbm, tc = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    res = {}
+
+    def timeit(fn, n=5, reps=10):
+        fn()
+        return statistics.median(ev_time_ms(lambda: [fn() for _ in range(reps)]) for _ in range(n)) / reps
+
+    def put(key, ms, byt=None, flops=None):
+        d = {"ms": round(ms, 4)}
+        if byt is not None:
+            d["of_hbm"] = round(byt / (ms / 1e3) / hbm, 3)
+        if flops is not None:
+            d["of_bf16_peak"] = round(flops / (ms / 1e3) / tc, 4)
+        res[key] = d
+
+    slot = eng.open_sequence()
+    eng.kv.reserve(slot, T + 1)
+    eng.kv.commit()
+    eb = 2
+    for tag, rows, start in (("prefill", T, 0), ("decode", 1, T)):
+        eng._workspace(rows)
+        row_ent = torch.zeros(rows, dtype=torch.int32, device=dev)
+        ent = torch.tensor([slot, 0, rows, start], dtype=torch.int32, device=dev)
+        x = torch.randn(rows, W, device=dev)
+        hn, he = torch.empty_like(x), torch.empty(rows, W, dtype=E, device=dev)
+        y1 = torch.randn(rows, W, device=dev).to(E)
+        idw = torch.rand(rows, device=dev)
+        Pm, Pd = eng.layers[li_m], eng.layers[li_d]
+        # between the output projection and the feed-forward: x += ls1 * y, norm2 -> fp32 (router) and bf16 (projections)
+        put(f"{tag}_close_mixer_norm", timeit(lambda: ops.layer_close(x, y1, ls=Pm["ls1"], w_next=Pm["norm2"], out_f=hn, out_e=he,
+                                                                      eps=1e-6)), byt=rows * W * (eb + 8 + 4 + eb))
+        # after the last layer's feed-forward: x += ls2 * (y + share * h), store the result, average over all results, norm
+        Pl = eng.layers[n_last - 1]
+        xs = eng._xs
+        put(f"{tag}_close_layer_average_norm",
+            timeit(lambda: ops.layer_close(x, y1, idw=idw, h_in=hn, ls=Pl["ls2"], xs=xs, n_prev=n_last, dwa=Pl["dwa"],
+                                           w_next=eng.w["final_norm"], out_e=he, eps=1e-6)),
+            byt=rows * W * (eb + 8 + 4 + 4 * n_last + 4 + eb))
+        if rows > 1:
+            put(f"{tag}_token_shift", timeit(lambda: ops.token_shift_ragged(hn, Pm["shift"], eng.slots[("shift", li_m)], row_ent,
+                                                                            ent, he)), byt=rows * W * (4 + eb))
+        else:
+            put(f"{tag}_close_layer_average_norm_shift",
+                timeit(lambda: ops.layer_close(x, y1, idw=idw, h_in=hn, ls=Pl["ls2"], xs=xs, n_prev=n_last - 1,
+                                               dwa=eng.layers[n_last - 2]["dwa"], w_next=Pl["norm1"], shift=Pl["shift"],
+                                               tail=eng.slots[("shift", n_last - 1)], ent=ent, out_e=he, eps=1e-6)),
+                byt=rows * W * (eb + 8 + 4 + 4 * (n_last - 1) + 4 + eb + 8))
+        # attention with the distance penalty (own cache: prep appends keys and values)
+        m = spec.layers[li_m].mixer
+        n_proj = Pm["w_proj"].shape[0]
+        proj = (0.5 * torch.randn(rows, n_proj, device=dev)).to(E)
+        qbuf = torch.empty(rows, m.heads * m.dim, device=dev)
+        mix = torch.empty(rows, m.heads * m.vdim, dtype=E, device=dev)
+        kc, vc = eng.kv.k[eng.kv_index[li_m]], eng.kv.v[eng.kv_index[li_m]]
+        off = Pm["off"]
+        put(f"{tag}_attn_prep", timeit(lambda: ops.attn_prep_append(proj, qbuf, kc, vc, row_ent, ent, eng.kv.page_table, m.heads,
+                                                                     m.kv_heads, m.dim, m.vdim, 0, off["q"], off["k"], off["v"],
+                                                                     None, None, 1e-6, None, None, None, None, bias=Pm["qkv_b"])))
+        blk = m.chunk if m.chunk else T
+        for pen in (True, False):
+            r1, r2 = (Pm["r1"], Pm["r2"]) if pen else (None, None)
+            key = f"{tag}_attn" + ("" if pen else "_without_penalty")
+            if rows > 1 and ops.attn_ragged_tc_supported(m.dim, m.vdim, E):
+                tiles = torch.tensor([[0, q0] for q0 in range(0, rows, 64)], dtype=torch.int32, device=dev)
+                ms = timeit(lambda: ops.attn_ragged_tc(qbuf, kc, vc, None, mix, ent, tiles, eng.kv.page_table, m.heads, m.kv_heads,
+                                                       m.dim, m.vdim, m.scale, chunk=m.chunk, r1=r1, r2=r2))
+                put(key, ms, flops=2 * (rows * blk // 2) * m.heads * (m.dim + m.vdim))
+            else:
+                splits = max(1, min(16, (4 * eng._sms) // (rows * m.heads), (blk + 31) // 32))
+                ms = timeit(lambda: ops.attn_ragged(qbuf, kc, vc, None, mix, row_ent, ent, eng.kv.page_table, m.heads, m.kv_heads,
+                                                    m.dim, m.vdim, m.scale, chunk=m.chunk, splits=splits,
+                                                    part=eng._apart_att if splits > 1 else None, r1=r1, r2=r2))
+                put(key, ms, byt=(start % blk + 1) * m.kv_heads * (m.dim + m.vdim) * eb)
+        # dense feed-forward with biases: the activation between the projections
+        F = spec.layers[li_d].ff
+        gu = (0.5 * torch.randn(rows, 2 * F, device=dev)).to(E)
+        act = torch.empty(rows, F, dtype=E, device=dev)
+        put(f"{tag}_ff_bias_silu_mul", timeit(lambda: ops.silu_mul(gu, act, bias=Pd["gu_b"])), byt=rows * F * 3 * eb)
+        # mixture of experts: router with groups, activation, projections
+        e = spec.layers[li_m].moe
+        wts = torch.empty(rows, e.experts, device=dev)
+        si = torch.empty(rows, e.top, dtype=torch.int32, device=dev)
+        sw = torch.empty(rows, e.top, device=dev)
+        put(f"{tag}_moe_route", timeit(lambda: ops.moe_route(hn, Pm["w_router"], Pm["corr"], wts, idw, si, sw, e.experts, e.top,
+                                                             groups=e.groups, keep=e.keep, wscale=e.route_scale, renorm=False)),
+            byt=rows * W * 4 + Pm["w_router"].numel() * 4)
+        gu = torch.empty(rows, Pm["w_gu"].shape[0], dtype=E, device=dev)
+        act = torch.empty(rows, e.total_ff, dtype=E, device=dev)
+        y2 = torch.empty(rows, W, dtype=E, device=dev)
+        ms_gu = timeit(lambda: eng._lin(he, Pm["w_gu"], gu), n=3, reps=3)
+        ms_act = timeit(lambda: ops.moe_act(gu, wts, act, e.experts, e.ff, 0.0, gated=False))
+        ms_dn = timeit(lambda: eng._lin(act, Pm["w_down"], y2), n=3, reps=3)
+        put(f"{tag}_moe_act", ms_act, byt=rows * e.total_ff * 2 * eb)
+        if rows > 1:
+            put(f"{tag}_moe_projections", ms_gu + ms_dn, flops=2 * rows * 2 * W * e.top * e.ff)
+            res[f"{tag}_moe_projections"]["of_bf16_peak_all_experts"] = round(2 * rows * 2 * W * e.total_ff / ((ms_gu + ms_dn) / 1e3) / tc, 4)
+        else:
+            put(f"{tag}_moe_projections_all_experts", ms_gu + ms_dn, byt=2 * W * e.total_ff * eb)
+            if ops.moe_sel_supported(W, e.ff, 0, e.top):
+                act_sel = torch.empty(rows, e.top * e.ff, dtype=E, device=dev)
+                ms = timeit(lambda: ops.moe_sel(he, Pm["w_gu"], Pm["w_down"], si, sw, act_sel, y2, e.experts, e.top, e.ff, 0.0,
+                                                gated=False))
+                put(f"{tag}_moe_chosen_experts", ms, byt=2 * W * e.top * e.ff * eb)
+    eng.close_sequence(slot)
+    return res
+
+
+
 def hybrid_kernel_times(eng, spec, T, peaks):
     """Each kernel of the ragged path alone at the step sizes of the comparison: a T-token portion (prefill) and one
     token after T (decode), against its algorithmic HBM bytes (or FLOPs) and the measured peaks."""
@@ -1033,6 +1209,8 @@ def main():
                     help="instead of the default workload: the Togalorn design beside the Sokevik design at equal sizes")
     ap.add_argument("--compare-fubepel", action="store_true",
                     help="instead of the default workload: the Fubepel design beside the Sokevik design at equal sizes")
+    ap.add_argument("--compare-gimudra", action="store_true",
+                    help="prefill / decode throughput of the Gimudra design beside the Togalorn and Sokevik designs at equal sizes")
     ap.add_argument("--hybrid-sizes", default="1b,8b")
     args = ap.parse_args()
 
@@ -1059,6 +1237,10 @@ def main():
     if args.compare_fubepel:
         if rank == 0:
             print(json.dumps(run_fubepel_compare(args, peaks)), flush=True)
+        return
+    if args.compare_gimudra:
+        if rank == 0:
+            print(json.dumps(run_gimudra_compare(args, peaks)), flush=True)
         return
     if world > 1 or args.gpus > 1:
         from dli_b200.pipeline import run_pipeline_bench
