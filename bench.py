@@ -1130,7 +1130,7 @@ def hybrid_kernel_times(eng, spec, T, peaks):
             byt = (start + 1) * m.kv_heads * (m.dim + m.vdim) * 2
             res[f"{tag}_attn"] = {"ms": round(ms, 4), "of_hbm": round(byt / (ms / 1e3) / hbm, 3)}
         else:
-            fl = 2 * (rows * rows // 2) * m.heads * (m.dim + m.vdim)
+            fl = 2 * (rows * (min(rows, m.chunk) if m.chunk else rows) // 2) * m.heads * (m.dim + m.vdim)  # visible pairs only
             res[f"{tag}_attn"] = {"ms": round(ms, 4), "of_bf16_peak": round(fl / (ms / 1e3) / (peaks["bf16_tflops"] * 1e12), 4)}
         # recurrent layer
         m, P = rec, eng.layers[li_r]

@@ -231,8 +231,9 @@ class RaggedEngine:
         self.prefill_chunk: Optional[int] = None   # tokens of a prompt per step (None: the scheduler's default)
         self.tc_min_rows = int(os.environ.get("DLI_RAGGED_TC_MIN_ROWS", "16"))  # portions from this size: tensor-core attention
         self.moe_sel_max_rows = 8                  # up to this many rows a step reads only the chosen experts' weights ...
-        self.moe_sel_share = 3.0                   # ... if they are at most 1/3 of all expert weights: the dense weight stream runs
-                                                   # at ~0.63 of the HBM peak, the gathered one at ~0.2 (measured, 2048-wide)
+        self.moe_sel_share = 3.0                   # ... if what the rows choose is at most 1/3 of all expert weights (gated
+        self.moe_sel_share_ungated = 4.5           # experts; 1/4.5 for experts without a gate): the dense weight stream runs at
+                                                   # ~0.62 of the HBM peak, the gathered one at ~0.18 / ~0.13 (measured, 2048-wide)
         self.delta_blocked = False                 # portions of prompts through the delta rule 16 rows at a time; off: row by row,
                                                    # which is faster while one sequence's columns leave a warp per scheduler
                                                    # (0.89 against 1.15 ms for 2 048 rows, 8 heads of 128 x 256)
@@ -911,8 +912,7 @@ class RaggedEngine:
             sel_idx, sel_w = self._sel_idx[:rows * e.top].view(rows, e.top), self._sel_w[:rows * e.top].view(rows, e.top)
             ops.moe_route(hn, P["w_router"], P["corr"], wts, idw, sel_idx, sel_w, e.experts, e.top, groups=e.groups,
                           keep=e.keep, wscale=e.route_scale, renorm=e.renorm)
-            if E == BF and rows <= self.moe_sel_max_rows and self.moe_sel_share * (e.top * e.ff + e.shared_ff) <= e.total_ff and \
-                    ops.moe_sel_supported(s.width, e.ff, e.shared_ff, e.top):
+            if self._moe_sel_ok(e, rows):
                 # decode rows of a sparse enough mixture: stream only the chosen experts' weights
                 n_sel = e.top * e.ff + e.shared_ff
                 ops.moe_sel(he, P["w_gu"], P["w_down"], sel_idx, sel_w, self._act[:rows * n_sel].view(rows, n_sel), y_last,
@@ -1019,8 +1019,7 @@ class RaggedEngine:
         idw = self._idw[:rows]
         ops.moe_route(hn, P["w_router"], P["corr"], wts, idw, self._sel_idx[:rows * e.top].view(rows, e.top),
                       self._sel_w[:rows * e.top].view(rows, e.top), e.experts, e.top)
-        if E == BF and rows <= self.moe_sel_max_rows and self.moe_sel_share * (e.top * e.ff + e.shared_ff) <= e.total_ff and \
-                ops.moe_sel_supported(s.width, e.ff, e.shared_ff, e.top):
+        if self._moe_sel_ok(e, rows):
             # decode rows of a sparse enough mixture: stream only the chosen experts' weights (and the shared expert's)
             n_sel = e.top * e.ff + e.shared_ff
             ops.moe_sel(he, P["w_gu"], P["w_down"], self._sel_idx[:rows * e.top].view(rows, e.top),
@@ -1035,6 +1034,14 @@ class RaggedEngine:
         ops.moe_act(gu, wts, act, e.experts, e.ff, e.limit, e.shared_ff, e.shared_limit, e.alpha)
         self._lin(act, P["w_down"], y2)
         ops.residual_add2(x, y, y2, idw if e.identity else None, hn if e.identity else None)
+
+    def _moe_sel_ok(self, e, rows) -> bool:
+        """Do the kernels that stream only the chosen experts' weights pay for a step of `rows` rows?  Every row streams its
+        own choice, so their traffic grows with the rows while the all-experts form reads every weight once."""
+        share = self.moe_sel_share if e.gated else self.moe_sel_share_ungated
+        return self.dtype == BF and rows <= self.moe_sel_max_rows and \
+            share * rows * (e.top * e.ff + e.shared_ff) <= e.total_ff and \
+            ops.moe_sel_supported(self.spec.width, e.ff, e.shared_ff, e.top)
 
     def _latent_attention(self, li, m, P, proj, mix, rows, views, tiles=False):
         """Decode rows and short portions: attention over the cached latents themselves — the heads' key up-projections

