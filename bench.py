@@ -955,7 +955,7 @@ def run_gimudra_compare(args, peaks):
 
 def gimudra_kernel_times(eng, spec, T, peaks):
     """Each kernel of the Gimudra mechanisms alone at the step sizes of the comparison: a T-token portion (prefill) and
-    one token after T (decode), against its algorithmic HBM bytes or FLOPs and the measured peaks."""
+    the prompt's last token alone (decode), against its algorithmic HBM bytes or FLOPs and the measured peaks."""
     from dli_b200 import ops
 
     dev, E, W = eng.device, eng.dtype, spec.width
@@ -981,7 +981,7 @@ def gimudra_kernel_times(eng, spec, T, peaks):
     eng.kv.reserve(slot, T + 1)
     eng.kv.commit()
     eb = 2
-    for tag, rows, start in (("prefill", T, 0), ("decode", 1, T)):
+    for tag, rows, start in (("prefill", T, 0), ("decode", 1, T - 1)):  # the decode row sees a whole block of keys
         eng._workspace(rows)
         row_ent = torch.zeros(rows, dtype=torch.int32, device=dev)
         ent = torch.tensor([slot, 0, rows, start], dtype=torch.int32, device=dev)
@@ -1093,7 +1093,7 @@ def hybrid_kernel_times(eng, spec, T, peaks):
         fn()
         return statistics.median(ev_time_ms(lambda: [fn() for _ in range(reps)]) for _ in range(n)) / reps
 
-    for tag, rows, start in (("prefill", T, 0), ("decode", 1, T)):
+    for tag, rows, start in (("prefill", T, 0), ("decode", 1, T - 1)):  # the decode row sees a whole block of keys
         row_ent = torch.zeros(rows, dtype=torch.int32, device=dev)
         ent = torch.tensor([slot, 0, rows, start], dtype=torch.int32, device=dev)
         x = torch.randn(rows, W, device=dev)
@@ -1127,7 +1127,7 @@ def hybrid_kernel_times(eng, spec, T, peaks):
                                              m.dim, m.vdim, m.scale, chunk=m.chunk, sink=P["sink"], g_off=off["g"], cos_v=cv, sin_v=sv)
         ms = timeit(run)
         if rows == 1:
-            byt = (start + 1) * m.kv_heads * (m.dim + m.vdim) * 2
+            byt = ((start % m.chunk if m.chunk else start) + 1) * m.kv_heads * (m.dim + m.vdim) * 2  # visible keys only
             res[f"{tag}_attn"] = {"ms": round(ms, 4), "of_hbm": round(byt / (ms / 1e3) / hbm, 3)}
         else:
             fl = 2 * (rows * (min(rows, m.chunk) if m.chunk else rows) // 2) * m.heads * (m.dim + m.vdim)  # visible pairs only

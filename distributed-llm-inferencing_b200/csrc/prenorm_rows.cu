@@ -51,8 +51,34 @@ struct LayerClose {
   int d;
 };
 
+// VEC consecutive channels per thread and load: 16-byte loads of the fp32 rows (8 bytes of bf16) when the width allows
+template <int VEC> __device__ __forceinline__ void ld_f(const float* p, float (&v)[VEC]);
+template <> __device__ __forceinline__ void ld_f<1>(const float* p, float (&v)[1]) { v[0] = *p; }
+template <> __device__ __forceinline__ void ld_f<4>(const float* p, float (&v)[4]) {
+  const float4 u = *reinterpret_cast<const float4*>(p);
+  v[0] = u.x; v[1] = u.y; v[2] = u.z; v[3] = u.w;
+}
+template <int VEC> __device__ __forceinline__ void st_f(float* p, const float (&v)[VEC]);
+template <> __device__ __forceinline__ void st_f<1>(float* p, const float (&v)[1]) { *p = v[0]; }
+template <> __device__ __forceinline__ void st_f<4>(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+template <int VEC> __device__ __forceinline__ void ld_e(const float* p, float (&v)[VEC]) { ld_f<VEC>(p, v); }
+template <int VEC> __device__ __forceinline__ void st_e(float* p, const float (&v)[VEC]) { st_f<VEC>(p, v); }
+template <int VEC> __device__ __forceinline__ void ld_e(const bf16* p, float (&v)[VEC]);
+template <> __device__ __forceinline__ void ld_e<1>(const bf16* p, float (&v)[1]) { v[0] = __bfloat162float(*p); }
+template <> __device__ __forceinline__ void ld_e<4>(const bf16* p, float (&v)[4]) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  v[0] = bf_lo(u.x); v[1] = bf_hi(u.x); v[2] = bf_lo(u.y); v[3] = bf_hi(u.y);
+}
+template <int VEC> __device__ __forceinline__ void st_e(bf16* p, const float (&v)[VEC]);
+template <> __device__ __forceinline__ void st_e<1>(bf16* p, const float (&v)[1]) { *p = __float2bfloat16_rn(v[0]); }
+template <> __device__ __forceinline__ void st_e<4>(bf16* p, const float (&v)[4]) {
+  *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]));
+}
+
 // One CTA per row.  Pass 1 forms the new x (and its sum of squares), pass 2 the next norm from the rows just written.
-template <typename E>
+template <typename E, int VEC>
 __global__ void __launch_bounds__(1024)
 layer_close_kernel(const E* __restrict__ y, float* __restrict__ x, E* __restrict__ out_e, LayerClose a) {
   __shared__ float red[32];
@@ -62,22 +88,54 @@ layer_close_kernel(const E* __restrict__ y, float* __restrict__ x, E* __restrict
   const size_t o = (size_t)row * d;
   const float iw = a.idw ? a.idw[row] : 0.f;
   float ss = 0.f;
-  for (int c = threadIdx.x; c < d; c += blockDim.x) {
-    float v = x[o + c];
+  for (int c = threadIdx.x * VEC; c < d; c += blockDim.x * VEC) {
+    float v[VEC];
+    ld_f<VEC>(x + o + c, v);
     if (y) {
-      float t = pn_to_f(y[o + c]);
-      if (a.bias) t += a.bias[c];
-      if (a.idw) t = fmaf(iw, a.h_in[o + c], t);
-      v = a.ls ? fmaf(a.ls[c], t, v) : v + t;
+      float t[VEC];
+      ld_e<VEC>(y + o + c, t);
+      if (a.bias) {
+        float b[VEC];
+        ld_f<VEC>(a.bias + c, b);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) t[i] += b[i];
+      }
+      if (a.idw) {
+        float h[VEC];
+        ld_f<VEC>(a.h_in + o + c, h);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) t[i] = fmaf(iw, h[i], t[i]);
+      }
+      if (a.ls) {
+        float l[VEC];
+        ld_f<VEC>(a.ls + c, l);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) v[i] = fmaf(l[i], t[i], v[i]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) v[i] += t[i];
+      }
     }
     if (a.dwa) {
-      a.xs[(size_t)a.n_prev * a.xs_stride + o + c] = v;
-      float u = 0.f;
-      for (int j = 0; j < a.n_prev; ++j) u = fmaf(a.dwa[j], a.xs[(size_t)j * a.xs_stride + o + c], u);
-      v = fmaf(a.dwa[a.n_prev], v, u);
+      st_f<VEC>(a.xs + (size_t)a.n_prev * a.xs_stride + o + c, v);
+      float u[VEC];
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) u[i] = 0.f;
+#pragma unroll 4
+      for (int j = 0; j < a.n_prev; ++j) {  // the earlier results' loads do not depend on one another
+        float p[VEC];
+        ld_f<VEC>(a.xs + (size_t)j * a.xs_stride + o + c, p);
+        const float w = a.dwa[j];
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) u[i] = fmaf(w, p[i], u[i]);
+      }
+      const float w = a.dwa[a.n_prev];
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) v[i] = fmaf(w, v[i], u[i]);
     }
-    if (y || a.dwa) x[o + c] = v;
-    ss = fmaf(v, v, ss);
+    if (y || a.dwa) st_f<VEC>(x + o + c, v);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) ss = fmaf(v[i], v[i], ss);
   }
   if (!a.w_next) return;
   ss = pn_block_sum(ss, red);  // its barriers also order the writes of x above before the reads below
@@ -87,16 +145,23 @@ layer_close_kernel(const E* __restrict__ y, float* __restrict__ x, E* __restrict
     const int4 e = reinterpret_cast<const int4*>(a.ent)[row];  // slot, first row (== row), 1, position
     slot = e.x; pos = e.w;
   }
-  for (int c = threadIdx.x; c < d; c += blockDim.x) {
-    float h = x[o + c] * r * a.w_next[c];
+  for (int c = threadIdx.x * VEC; c < d; c += blockDim.x * VEC) {
+    float h[VEC], w[VEC];
+    ld_f<VEC>(x + o + c, h);
+    ld_f<VEC>(a.w_next + c, w);
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) h[i] = h[i] * r * w[i];
     if (a.shift) {
       float* t = a.tail + (size_t)slot * d + c;
-      const float prev = pos > 0 ? *t : 0.f;
-      *t = h;
-      h = fmaf(prev - h, a.shift[c], h);
+      float prev[VEC], s[VEC];
+      ld_f<VEC>(t, prev);
+      ld_f<VEC>(a.shift + c, s);
+      st_f<VEC>(t, h);
+#pragma unroll
+      for (int i = 0; i < VEC; ++i) h[i] = fmaf((pos > 0 ? prev[i] : 0.f) - h[i], s[i], h[i]);
     }
-    if (a.out_f) a.out_f[o + c] = h;
-    if (out_e) out_e[o + c] = pn_from_f<E>(h);
+    if (a.out_f) st_f<VEC>(a.out_f + o + c, h);
+    if (out_e) st_e<VEC>(out_e + o + c, h);
   }
 }
 
@@ -149,9 +214,20 @@ int dli_layer_close(const void* y, const float* bias, const float* idw, const fl
   if (rows <= 0) return DLI_OK;
   LayerClose a{bias, idw, h_in, ls, xs, xs_stride, n_prev, dwa, w_next, shift, tail, ent, out_f, eps, d};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int th = (rows <= 64 && d >= 2048) ? 1024 : 256;
-  if (dt == 0) DLI_LAUNCH("layer_close", layer_close_kernel<bf16>, dim3(rows), dim3(th), 0, s, (const bf16*)y, x, (bf16*)out_e, a);
-  else DLI_LAUNCH("layer_close", layer_close_kernel<float>, dim3(rows), dim3(th), 0, s, (const float*)y, x, (float*)out_e, a);
+  // 16-byte accesses when every row and vector starts on such a boundary
+  auto al = [](const void* p, uintptr_t n) { return (reinterpret_cast<uintptr_t>(p) & (n - 1)) == 0; };
+  const bool vec = d % 4 == 0 && al(x, 16) && al(y, dt == 0 ? 8 : 16) && al(bias, 16) && al(h_in, 16) && al(ls, 16) && al(xs, 16) &&
+                   xs_stride % 4 == 0 && al(w_next, 16) && al(shift, 16) && al(tail, 16) && al(out_f, 16) &&
+                   al(out_e, dt == 0 ? 8 : 16);
+  const int per = vec ? 4 : 1;
+  const int th = (rows <= 64 && d >= 2048 * per) ? 1024 : (d >= 256 * per ? 256 : 128);
+  if (dt == 0) {
+    if (vec) DLI_LAUNCH("layer_close", (layer_close_kernel<bf16, 4>), dim3(rows), dim3(th), 0, s, (const bf16*)y, x, (bf16*)out_e, a);
+    else DLI_LAUNCH("layer_close", (layer_close_kernel<bf16, 1>), dim3(rows), dim3(th), 0, s, (const bf16*)y, x, (bf16*)out_e, a);
+  } else {
+    if (vec) DLI_LAUNCH("layer_close", (layer_close_kernel<float, 4>), dim3(rows), dim3(th), 0, s, (const float*)y, x, (float*)out_e, a);
+    else DLI_LAUNCH("layer_close", (layer_close_kernel<float, 1>), dim3(rows), dim3(th), 0, s, (const float*)y, x, (float*)out_e, a);
+  }
   return DLI_OK;
 }
 

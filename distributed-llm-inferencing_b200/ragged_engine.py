@@ -496,8 +496,8 @@ class RaggedEngine:
         if any(L.parallel or L.pre_norm for L in s.layers):
             self._he = torch.empty(rows, s.width, dtype=E, device=dev)
             self._y2 = torch.empty(rows, s.width, dtype=E, device=dev)
-        if any(L.pre_norm and L.token_shift for L in s.layers):
-            self._hs = torch.empty(rows, s.width, dtype=f32, device=dev)  # normed rows before the token shift
+        if any(L.pre_norm for L in s.layers):
+            self._hs = torch.empty(rows, s.width, dtype=f32, device=dev)  # normed rows before the token shift / after the last norm
         if any(L.pre_norm and L.depth_avg for L in s.layers):
             # the embedding output and every layer's result, for the averages after the layers
             self._xs = torch.empty(s.n_layers + 1, rows, s.width, dtype=f32, device=dev)
@@ -779,7 +779,7 @@ class RaggedEngine:
         if nw == 0:
             return None
         hw = self._hw[:nw] if nw <= self._hw.shape[0] else torch.empty(nw, W, dtype=E, device=dev)
-        ops.gather_cast(hn, d_want, hw)
+        ops.gather_cast(self._hs[:rows] if final_done else hn, d_want, hw)
         vp = self.w["head"].shape[0]
         logits = logits_out[:nw] if logits_out is not None else torch.empty(nw, vp, dtype=E, device=dev)
         self._lin(hw, self.w["head"], logits)
@@ -933,7 +933,7 @@ class RaggedEngine:
         if kind == "layer":
             open_mixer({"norm1": w_next, "shift": shift_next}, tail_next, y_last, **close)
         elif kind == "final":
-            ops.layer_close(x, y_last, w_next=w_next, out_f=hn, eps=s.eps, **close)
+            ops.layer_close(x, y_last, w_next=w_next, out_f=self._hs[:rows], eps=s.eps, **close)
         else:
             ops.layer_close(x, y_last, eps=s.eps, **close)
 

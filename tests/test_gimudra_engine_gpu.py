@@ -60,7 +60,7 @@ def cfg_b():
     return config([(attention(heads=1, kv_heads=1, dim=6, vdim=4, scale=0.9, size=1), moe(experts=5, identity=1, top=2, count=3, keep=1, ff=8, scale=2.0)),
                    (attention(heads=3, kv_heads=1, dim=4, vdim=6, scale=0.4, size=0), dense(ff=20)),
                    (attention(heads=3, kv_heads=1, dim=4, vdim=6, scale=0.4, size=3, kv_from=1), moe(experts=1, identity=1, top=1, count=2, keep=2, ff=16, scale=1.0)),
-                   (attention(heads=2, kv_heads=2, dim=2, vdim=2, scale=1.0, size=64), None)],
+                   (attention(heads=2, kv_heads=2, dim=2, vdim=2, scale=1.0, size=50), None)],
                   width=40, vocab=53, scale=1.0)
 
 
@@ -154,7 +154,7 @@ def test_residual_stream_after_every_layer(make):
 @pytest.mark.parametrize("cuts", [[], [1, 1, 2], [2, 2, 3, 5, 7, 11], [17, 2, 16, 3], [30]])
 def test_portions_and_decoding_float32(make, cuts):
     """Token by token from the first token; portions of 2..; a prompt then decoding over page borders and over the edges
-    of blocks of 1, 3, 5, 6, 7, 9, 13 and 32 positions."""
+    of blocks of 1, 3, 5, 6, 7, 9, 13, 32 and 50 positions."""
     cfg = make()
     eng, sd = build(cfg, torch.float32)
     toks = prompt(52, cfg["vocab"], 3)

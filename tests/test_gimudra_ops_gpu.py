@@ -353,7 +353,7 @@ def route_kernel(h, w, c, n_real, top, groups, keep, scale):
     return wts.cpu(), idw.cpu(), si.cpu(), sw.cpu()
 
 
-@pytest.mark.parametrize("shape", [(12, 4, 3, 4, 2, 2.0), (6, 2, 2, 4, 3, 0.5), (5, 0, 5, 1, 1, 1.0), (4, 4, 2, 2, 1, 1.0),
+@pytest.mark.parametrize("shape", [(10, 2, 3, 4, 2, 2.5), (6, 2, 2, 4, 3, 0.5), (5, 0, 5, 1, 1, 1.0), (4, 4, 2, 2, 1, 1.0),
                                    (9, 0, 3, 3, 3, 3.0)])
 def test_router_with_groups_against_oracle(shape):
     """(experts, pass-through outputs, top, groups, kept groups, scale): negative choice scores throughout (a group set
