@@ -1054,7 +1054,7 @@ def gimudra_kernel_times(eng, spec, T, peaks):
         ms_gu = timeit(lambda: eng._lin(he, Pm["w_gu"], gu), n=3, reps=3)
         ms_act = timeit(lambda: ops.moe_act(gu, wts, act, e.experts, e.ff, 0.0, gated=False))
         ms_dn = timeit(lambda: eng._lin(act, Pm["w_down"], y2), n=3, reps=3)
-        put(f"{tag}_moe_act", ms_act, byt=rows * e.total_ff * 2 * eb)
+        put(f"{tag}_moe_act", ms_act, byt=rows * (e.total_ff + e.top * e.ff) * eb)  # written: all experts; read: the chosen ones
         if rows > 1:
             put(f"{tag}_moe_projections", ms_gu + ms_dn, flops=2 * rows * 2 * W * e.top * e.ff)
             res[f"{tag}_moe_projections"]["of_bf16_peak_all_experts"] = round(2 * rows * 2 * W * e.total_ff / ((ms_gu + ms_dn) / 1e3) / tc, 4)

@@ -144,6 +144,7 @@ struct MoeAct {
   float alpha;              // g * sigmoid(alpha * g)
   int ld;                   // row stride of gu
   int mode;                 // 0: clamped gated form; 1: no gate, max(u, 0)^2, columns [e*ff, +ff) of gu (shared: after them)
+  int vec;                  // mode 1: sizes and pointers allow 16-byte accesses
 };
 
 // act[row, e*ff + f] and act[row, n_exp*ff + f] (shared); a row's channels go to one CTA, or to several for few rows.
@@ -156,6 +157,32 @@ moe_act_kernel(const E* __restrict__ gu, const float* __restrict__ wts, E* __res
   const E* g = gu + row * a.ld;
   const int F = a.n_exp * a.ff + a.ff_s;
   E* out = act + row * F;
+  if (a.mode == 1 && a.vec) {
+    // experts without a gate, 16 bytes per thread and access: the V elements lie in one expert (ff, ff_s multiples of V)
+    constexpr int V = 16 / (int)sizeof(E);
+    for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * V; i < F; i += blockDim.x * gridDim.y * V) {
+      const float wt = i < a.n_exp * a.ff ? wts[row * a.n_exp + i / a.ff] : 1.f;
+      uint4 o = make_uint4(0, 0, 0, 0);
+      if (wt != 0.f) {
+        const uint4 u = *reinterpret_cast<const uint4*>(g + i);
+        if constexpr (sizeof(E) == 2) {
+          float f[8];
+          unpack8(u, f);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) { const float r = fmaxf(f[k], 0.f); f[k] = r * r * wt; }
+          o = pack8(f);
+        } else {
+          const float f[4] = {__uint_as_float(u.x), __uint_as_float(u.y), __uint_as_float(u.z), __uint_as_float(u.w)};
+          float r[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) { const float t = fmaxf(f[k], 0.f); r[k] = t * t * wt; }
+          o = make_uint4(__float_as_uint(r[0]), __float_as_uint(r[1]), __float_as_uint(r[2]), __float_as_uint(r[3]));
+        }
+      }
+      *reinterpret_cast<uint4*>(out + i) = o;
+    }
+    return;
+  }
   for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < F; i += blockDim.x * gridDim.y) {
     float gv, uv, lim, wt;
     if (a.mode == 1) {
@@ -364,9 +391,12 @@ int dli_moe_act(const void* gu, const float* wts, void* act, int rows, int n_exp
                 "dli_moe_act: null pointer or bad shape");
   DLI_CHECK_ARG(dt == 0 || dt == 1, "element type %d: 0 = bf16, 1 = float", dt);
   if (rows <= 0) return DLI_OK;
-  MoeAct a{n_exp, ff, limit, ff_s, limit_s, alpha, ld, mode};
+  const int per = dt == 0 ? 8 : 4;
+  const int vec = mode == 1 && ff % per == 0 && ff_s % per == 0 && ld % per == 0 && aligned16(gu) && aligned16(act);
+  MoeAct a{n_exp, ff, limit, ff_s, limit_s, alpha, ld, mode, vec};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int gy = rows <= 64 ? min(64, (n_exp * ff + ff_s + 255) / 256) : 1;  // few rows: a row's channels over several CTAs
+  const int work = (n_exp * ff + ff_s) / (vec ? per : 1);
+  const int gy = rows <= 64 ? min(64, (work + 255) / 256) : (work >= 4096 ? 4 : 1);  // few rows, or long rows: several CTAs per row
   if (dt == 0) DLI_LAUNCH("moe_act", moe_act_kernel<bf16>, dim3(rows, gy), dim3(256), 0, s, (const bf16*)gu, wts, (bf16*)act, a);
   else DLI_LAUNCH("moe_act", moe_act_kernel<float>, dim3(rows, gy), dim3(256), 0, s, (const float*)gu, wts, (float*)act, a);
   return DLI_OK;
@@ -383,7 +413,7 @@ int dli_moe_sel_bf16(const void* x, const void* w_gu, const void* w_down, const 
   DLI_CHECK_ARG(n_exp >= 0 && top >= 0 && dli_moe_sel_supported(d, ff, ff_s, top) && aligned16(w_gu) && aligned16(w_down),
                 "dli_moe_sel_bf16: sizes d=%d ff=%d ff_s=%d must be multiples of 8 and fit shared memory", d, ff, ff_s);
   if (rows <= 0) return DLI_OK;
-  MoeAct a{n_exp, ff, limit, ff_s, limit_s, alpha, 0, mode};
+  MoeAct a{n_exp, ff, limit, ff_s, limit_s, alpha, 0, mode, 0};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   static PerDeviceOnce once_a, once_d;
   DLI_ONCE_PER_DEVICE(once_a, dev, DLI_CUDA_CALL(cudaFuncSetAttribute(moe_sel_act_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024)));

@@ -231,9 +231,11 @@ class RaggedEngine:
         self.prefill_chunk: Optional[int] = None   # tokens of a prompt per step (None: the scheduler's default)
         self.tc_min_rows = int(os.environ.get("DLI_RAGGED_TC_MIN_ROWS", "16"))  # portions from this size: tensor-core attention
         self.moe_sel_max_rows = 8                  # up to this many rows a step reads only the chosen experts' weights ...
-        self.moe_sel_share = 3.0                   # ... if what the rows choose is at most 1/3 of all expert weights (gated
-        self.moe_sel_share_ungated = 4.5           # experts; 1/4.5 for experts without a gate): the dense weight stream runs at
-                                                   # ~0.62 of the HBM peak, the gathered one at ~0.18 / ~0.13 (measured, 2048-wide)
+        self.moe_sel_share = 3.0                   # ... if what the rows choose is at most 1/3 of all expert weights ...
+        self.moe_sel_min_bytes = 512 << 20         # ... and a layer's experts are at least this large: the two gathering kernels
+                                                   # take ~75 us whatever they read, the stream over all experts runs at 0.6-0.95
+                                                   # of the HBM peak (measured: 235 MB of experts, 4 of 14 chosen: 81 against 69 us;
+                                                   # 822 MB: 100 against 143 us)
         self.delta_blocked = False                 # portions of prompts through the delta rule 16 rows at a time; off: row by row,
                                                    # which is faster while one sequence's columns leave a warp per scheduler
                                                    # (0.89 against 1.15 ms for 2 048 rows, 8 heads of 128 x 256)
@@ -1038,9 +1040,9 @@ class RaggedEngine:
     def _moe_sel_ok(self, e, rows) -> bool:
         """Do the kernels that stream only the chosen experts' weights pay for a step of `rows` rows?  Every row streams its
         own choice, so their traffic grows with the rows while the all-experts form reads every weight once."""
-        share = self.moe_sel_share if e.gated else self.moe_sel_share_ungated
-        return self.dtype == BF and rows <= self.moe_sel_max_rows and \
-            share * rows * (e.top * e.ff + e.shared_ff) <= e.total_ff and \
+        total_bytes = e.total_ff * self.spec.width * (3 if e.gated else 2) * 2
+        return self.dtype == BF and rows <= self.moe_sel_max_rows and total_bytes >= self.moe_sel_min_bytes and \
+            self.moe_sel_share * rows * (e.top * e.ff + e.shared_ff) <= e.total_ff and \
             ops.moe_sel_supported(self.spec.width, e.ff, e.shared_ff, e.top)
 
     def _latent_attention(self, li, m, P, proj, mix, rows, views, tiles=False):

@@ -186,6 +186,8 @@ def test_bfloat16_sizes_of_the_tensor_core_kernels():
                  width=128, vocab=200)
     eng, sd = build(cfg, torch.bfloat16, max_seq_len=256, page_size=16, pool=512, std=0.08)
     from dli_b200 import ops
+    assert not eng._moe_sel_ok(eng.spec.layers[1].moe, 1)
+    eng.moe_sel_min_bytes = 0                     # the engine keeps the chosen-experts kernels for large mixtures; here they run
     assert all(eng._moe_sel_ok(eng.spec.layers[i].moe, 1) and not eng._moe_sel_ok(eng.spec.layers[i].moe, 3) for i in (1, 2))
     assert all(ops.attn_ragged_tc_supported(L.mixer.dim, L.mixer.vdim, torch.bfloat16) for L in eng.spec.layers)
     toks = prompt(230, cfg["vocab"], 6)

@@ -329,7 +329,8 @@ def test_bfloat16_decode_rows_of_a_sparse_mixture_read_only_the_chosen_experts()
                   (latent(), moe(experts=8, identity=0, top=1, ff=16, shared=(8, 1.0)))], width=64)
     eng, sd = build(cfg, torch.bfloat16)
     e = eng.spec.layers[0].moe
-    assert eng.moe_sel_share * (e.top * e.ff + e.shared_ff) <= e.total_ff
+    eng.moe_sel_min_bytes = 0                     # the engine keeps these kernels for large mixtures; here they run at a small one
+    assert eng._moe_sel_ok(e, 1)
     toks = prompt(40, cfg["vocab"], 8)
     ref, _ = R.forward(cfg, sd, toks)
     whole = run_schedule(eng, toks, [40])
