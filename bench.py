@@ -993,6 +993,16 @@ def gimudra_kernel_times(eng, spec, T, peaks):
         # between the output projection and the feed-forward: x += ls1 * y, norm2 -> fp32 (router) and bf16 (projections)
         put(f"{tag}_close_mixer_norm", timeit(lambda: ops.layer_close(x, y1, ls=Pm["ls1"], w_next=Pm["norm2"], out_f=hn, out_e=he,
                                                                       eps=1e-6)), byt=rows * W * (eb + 8 + 4 + eb))
+        # the same kernel with the router of the mixture that follows (what the engine launches in front of the experts)
+        e = spec.layers[li_m].moe
+        wts = torch.empty(rows, e.experts, device=dev)
+        si = torch.empty(rows, e.top, dtype=torch.int32, device=dev)
+        sw = torch.empty(rows, e.top, device=dev)
+        route = dict(w_router=Pm["w_router"], correction=Pm["corr"], wts=wts, idw=idw, sel_idx=si, sel_w=sw, n_real=e.experts,
+                     top=e.top, groups=e.groups, keep=e.keep, wscale=e.route_scale, renorm=False)
+        put(f"{tag}_close_mixer_norm_route", timeit(lambda: ops.layer_close(x, y1, ls=Pm["ls1"], w_next=Pm["norm2"], out_f=hn,
+                                                                            out_e=he, eps=1e-6, route=route)),
+            byt=rows * W * (eb + 8 + 4 + eb) + Pm["w_router"].numel() * 4)
         # after the last layer's feed-forward: x += ls2 * (y + share * h), store the result, average over all results, norm
         Pl = eng.layers[n_last - 1]
         xs = eng._xs
@@ -1041,10 +1051,6 @@ def gimudra_kernel_times(eng, spec, T, peaks):
         act = torch.empty(rows, F, dtype=E, device=dev)
         put(f"{tag}_ff_bias_silu_mul", timeit(lambda: ops.silu_mul(gu, act, bias=Pd["gu_b"])), byt=rows * F * 3 * eb)
         # mixture of experts: router with groups, activation, projections
-        e = spec.layers[li_m].moe
-        wts = torch.empty(rows, e.experts, device=dev)
-        si = torch.empty(rows, e.top, dtype=torch.int32, device=dev)
-        sw = torch.empty(rows, e.top, device=dev)
         put(f"{tag}_moe_route", timeit(lambda: ops.moe_route(hn, Pm["w_router"], Pm["corr"], wts, idw, si, sw, e.experts, e.top,
                                                              groups=e.groups, keep=e.keep, wscale=e.route_scale, renorm=False)),
             byt=rows * W * 4 + Pm["w_router"].numel() * 4)

@@ -105,7 +105,7 @@ SIGNATURES = {
     "dli_attn_ragged_tc": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _f, _i, _i, _i, _vp, _i,
                                 _i, _vp, _vp, _vp, _vp, _vp]),
     "dli_layer_close": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _f, _i,
-                             _vp]),
+                             _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _vp]),
     "dli_token_shift_ragged": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp]),
     "dli_postnorm_vec_add": (_i, [_vp, _vp, _vp, _vp, _i, _i, _f, _i, _vp]),
     "dli_token_side_act": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),

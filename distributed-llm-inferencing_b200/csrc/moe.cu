@@ -16,6 +16,7 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "moe_route.cuh"
 
 namespace dli {
 
@@ -26,114 +27,13 @@ template <typename E> __device__ __forceinline__ E x_from_f(float v);
 template <> __device__ __forceinline__ float x_from_f<float>(float v) { return v; }
 template <> __device__ __forceinline__ bf16 x_from_f<bf16>(float v) { return __float2bfloat16_rn(v); }
 
-// One CTA per row: a warp per router output for the logits, then one warp does the softmax and the choice.
+// One CTA per row: a warp per router output for the logits, then one warp does the softmax and the choice (moe_route.cuh).
 __global__ void __launch_bounds__(512)
-moe_route_kernel(const float* __restrict__ h, const float* __restrict__ wr, const float* __restrict__ corr,
-                 float* __restrict__ wts, float* __restrict__ idw, int32_t* __restrict__ sel_idx,
-                 float* __restrict__ sel_w, int d, int n_out, int n_real, int top, int groups, int keep, float wscale,
-                 int renorm) {
+moe_route_kernel(const float* __restrict__ h, int d, RouteArgs ra) {
   extern __shared__ float zs[];  // [n_out] scores, [n_out] choice scores, [groups] group scores
-  float* cs = zs + n_out;
-  float* gm = cs + n_out;
   pdl_wait();
   pdl_trigger();
-  const size_t row = blockIdx.x;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  const float* hr = h + row * d;
-  for (int o = warp; o < n_out; o += nw) {
-    const float* w = wr + (size_t)o * d;
-    float acc = 0.f;
-    if ((d & 3) == 0) {  // 16-byte loads, four in flight per lane
-      const float4* h4 = reinterpret_cast<const float4*>(hr);
-      const float4* w4 = reinterpret_cast<const float4*>(w);
-#pragma unroll 4
-      for (int c = lane; c < d / 4; c += 32) {
-        const float4 a = h4[c], b = w4[c];
-        acc = fmaf(a.x, b.x, acc); acc = fmaf(a.y, b.y, acc); acc = fmaf(a.z, b.z, acc); acc = fmaf(a.w, b.w, acc);
-      }
-    } else {
-      for (int c = lane; c < d; c += 32) acc = fmaf(hr[c], w[c], acc);
-    }
-    acc = warp_sum(acc);
-    if (lane == 0) zs[o] = acc;
-  }
-  __syncthreads();
-  if (warp != 0) return;
-  float mx = -INFINITY;
-  for (int o = lane; o < n_out; o += 32) mx = fmaxf(mx, zs[o]);
-  mx = warp_max(mx);
-  float sum = 0.f;
-  for (int o = lane; o < n_out; o += 32) sum += expf(zs[o] - mx);
-  sum = warp_sum(sum);
-  for (int o = lane; o < n_out; o += 32) {
-    const float s = expf(zs[o] - mx) / sum;
-    zs[o] = s;
-    cs[o] = s + (corr ? corr[o] : 0.f);
-    if (o < n_real) wts[row * n_real + o] = 0.f;
-  }
-  __syncwarp();
-  if (groups > 1) {
-    // a group's score is its largest choice score; the groups that are not among the `keep` best leave the choice
-    const int per = n_out / groups;
-    for (int g = lane; g < groups; g += 32) {
-      float b = -INFINITY;
-      for (int o = g * per; o < (g + 1) * per; ++o) b = fmaxf(b, cs[o]);
-      gm[g] = b;
-    }
-    __syncwarp();
-    for (int k = 0; k < keep; ++k) {
-      float best = -INFINITY;
-      int bi = 0x7fffffff;
-      for (int g = lane; g < groups; g += 32) {
-        const float c = gm[g];
-        if (c > best && c != INFINITY) { best = c; bi = g; }
-      }
-      for (int off = 16; off > 0; off >>= 1) {
-        const float ob = __shfl_xor_sync(0xffffffffu, best, off);
-        const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
-        if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
-      }
-      if (lane == 0 && bi < groups) gm[bi] = INFINITY;  // kept
-      __syncwarp();
-    }
-    for (int o = lane; o < n_out; o += 32)
-      if (gm[o / per] != INFINITY) cs[o] = -INFINITY;
-    __syncwarp();
-  }
-  // the `top` largest choice scores, one at a time (lowest index wins a tie)
-  float chosen_sum = 0.f;
-  for (int k = 0; k < top; ++k) {
-    float best = -INFINITY;
-    int bi = 0x7fffffff;
-    for (int o = lane; o < n_out; o += 32) {
-      const float c = cs[o];
-      if (c > best) { best = c; bi = o; }
-    }
-    for (int off = 16; off > 0; off >>= 1) {
-      const float ob = __shfl_xor_sync(0xffffffffu, best, off);
-      const int oi = __shfl_xor_sync(0xffffffffu, bi, off);
-      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
-    }
-    if (bi >= n_out) bi = 0;  // fewer candidates than `top` (every score -inf or NaN): stay inside the row
-    if (lane == 0) {
-      cs[bi] = -INFINITY;
-      sel_idx[row * top + k] = bi;
-    }
-    chosen_sum += zs[bi];
-    __syncwarp();
-  }
-  const float inv = (renorm ? 1.f / (chosen_sum + 1e-20f) : 1.f) * wscale;
-  if (lane == 0) {
-    float ident = 0.f;
-    for (int k = 0; k < top; ++k) {
-      const int o = sel_idx[row * top + k];
-      const float w = zs[o] * inv;
-      sel_w[row * top + k] = w;
-      if (o < n_real) wts[row * n_real + o] = w;
-      else ident += w;
-    }
-    idw[row] = ident;
-  }
+  moe_route_row(h + (size_t)blockIdx.x * d, d, blockIdx.x, ra, zs);
 }
 
 struct MoeAct {
@@ -378,9 +278,9 @@ int dli_moe_route(const float* h, const float* w_router, const float* correction
   DLI_CHECK_ARG(d > 0 && n_out > 0 && n_real >= 0 && n_real <= n_out && top > 0 && top <= n_out && n_out <= 4096,
                 "dli_moe_route: %d router outputs (%d real experts), top %d", n_out, n_real, top);
   if (rows <= 0) return DLI_OK;
+  RouteArgs ra{w_router, correction, wts, idw, sel_idx, sel_w, n_out, n_real, top, groups, keep, wscale, renorm};
   DLI_LAUNCH("moe_route", moe_route_kernel, dim3(rows), dim3(rows <= 64 ? 512 : 256), (size_t)(2 * n_out + groups) * sizeof(float),
-             static_cast<cudaStream_t>(stream), h, w_router, correction, wts, idw, sel_idx, sel_w, d, n_out, n_real, top,
-             groups, keep, wscale, renorm);
+             static_cast<cudaStream_t>(stream), h, d, ra);
   return DLI_OK;
 }
 

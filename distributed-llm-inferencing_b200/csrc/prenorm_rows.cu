@@ -9,9 +9,11 @@
 // dli_layer_close does everything between two projections in one pass over the row: the scaled residual add (with an
 // optional bias on the sublayer's result and the share of pass-through experts), the depth average, and the NEXT
 // norm (fp32 and / or element-type output).  For steps of one row per entry (decode) it also applies the next mixer's
-// token shift and advances the slot's previous row.  dli_token_shift_ragged is the shift for steps with portions of
-// prompts, on the normed rows.
+// token shift and advances the slot's previous row; where the norm feeds a mixture of experts it also runs the ROUTER on
+// the normed row it has just written.  dli_token_shift_ragged is the shift for steps with portions of prompts, on the
+// normed rows.
 #include "common.cuh"
+#include "moe_route.cuh"
 
 namespace dli {
 
@@ -49,6 +51,8 @@ struct LayerClose {
   float* out_f;           // [rows, d] or NULL
   float eps;
   int d;
+  int has_route;          // the router of the feed-forward that follows runs on out_f's row
+  RouteArgs route;
 };
 
 // VEC consecutive channels per thread and load: 16-byte loads of the fp32 rows (8 bytes of bf16) when the width allows
@@ -163,6 +167,11 @@ layer_close_kernel(const E* __restrict__ y, float* __restrict__ x, E* __restrict
     if (a.out_f) st_f<VEC>(a.out_f + o + c, h);
     if (out_e) st_e<VEC>(out_e + o + c, h);
   }
+  if (a.has_route) {
+    extern __shared__ float route_scratch[];  // 2 * n_out + groups floats
+    __syncthreads();                          // the row of out_f is complete
+    moe_route_row(a.out_f + o, d, row, a.route, route_scratch);
+  }
 }
 
 // out[row] = h[row] + (prev - h[row]) * s with prev the previous row of the same entry, or, for an entry's first row, the
@@ -201,6 +210,8 @@ extern "C" {
 int dli_layer_close(const void* y, const float* bias, const float* idw, const float* h_in, const float* ls, float* x,
                     float* xs, size_t xs_stride, int n_prev, const float* dwa, const float* w_next, const float* shift,
                     float* tail, const int32_t* ent, float* out_f, void* out_e, int rows, int d, float eps, int dt,
+                    const float* w_router, const float* correction, float* r_wts, float* r_idw, int32_t* r_sel_idx,
+                    float* r_sel_w, int n_out, int n_real, int top, int groups, int keep, float wscale, int renorm,
                     dli_stream_t stream) {
   DLI_CHECK_ARG(x && d > 0, "dli_layer_close: null pointer or empty shape");
   DLI_CHECK_ARG(y || !(bias || idw || ls), "dli_layer_close: bias, pass-through share and layer scale need a sublayer result");
@@ -211,8 +222,16 @@ int dli_layer_close(const void* y, const float* bias, const float* idw, const fl
   DLI_CHECK_ARG(!shift || (tail && ent && (reinterpret_cast<uintptr_t>(ent) & 15u) == 0),
                 "dli_layer_close: the token shift needs the slots' rows and a 16-byte aligned ent");
   DLI_CHECK_ARG(dt == 0 || dt == 1, "element type %d: 0 = bf16, 1 = float", dt);
+  if (groups < 1) groups = 1;
+  DLI_CHECK_ARG(!w_router || (out_f && !shift && r_wts && r_idw && r_sel_idx && r_sel_w && n_out > 0 && n_out <= 4096 &&
+                              n_real >= 0 && n_real <= n_out && top > 0 && top <= n_out &&
+                              (groups == 1 || (n_out % groups == 0 && keep >= 1 && keep <= groups && keep * (n_out / groups) >= top))),
+                "dli_layer_close: the router needs the fp32 normed rows (no shift) and its outputs; %d outputs (%d real), top %d, "
+                "%d groups of which %d are kept", n_out, n_real, top, groups, keep);
   if (rows <= 0) return DLI_OK;
-  LayerClose a{bias, idw, h_in, ls, xs, xs_stride, n_prev, dwa, w_next, shift, tail, ent, out_f, eps, d};
+  LayerClose a{bias, idw, h_in, ls, xs, xs_stride, n_prev, dwa, w_next, shift, tail, ent, out_f, eps, d, w_router ? 1 : 0,
+               RouteArgs{w_router, correction, r_wts, r_idw, r_sel_idx, r_sel_w, n_out, n_real, top, groups, keep, wscale, renorm}};
+  const size_t smem = w_router ? (size_t)(2 * n_out + groups) * sizeof(float) : 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   // 16-byte accesses when every row and vector starts on such a boundary
   auto al = [](const void* p, uintptr_t n) { return (reinterpret_cast<uintptr_t>(p) & (n - 1)) == 0; };
@@ -220,13 +239,14 @@ int dli_layer_close(const void* y, const float* bias, const float* idw, const fl
                    xs_stride % 4 == 0 && al(w_next, 16) && al(shift, 16) && al(tail, 16) && al(out_f, 16) &&
                    al(out_e, dt == 0 ? 8 : 16);
   const int per = vec ? 4 : 1;
-  const int th = (rows <= 64 && d >= 2048 * per) ? 1024 : (d >= 256 * per ? 256 : 128);
+  int th = (rows <= 64 && d >= 2048 * per) ? 1024 : (d >= 256 * per ? 256 : 128);
+  if (w_router && th < 256) th = 256;  // a warp per router output
   if (dt == 0) {
-    if (vec) DLI_LAUNCH("layer_close", (layer_close_kernel<bf16, 4>), dim3(rows), dim3(th), 0, s, (const bf16*)y, x, (bf16*)out_e, a);
-    else DLI_LAUNCH("layer_close", (layer_close_kernel<bf16, 1>), dim3(rows), dim3(th), 0, s, (const bf16*)y, x, (bf16*)out_e, a);
+    if (vec) DLI_LAUNCH("layer_close", (layer_close_kernel<bf16, 4>), dim3(rows), dim3(th), smem, s, (const bf16*)y, x, (bf16*)out_e, a);
+    else DLI_LAUNCH("layer_close", (layer_close_kernel<bf16, 1>), dim3(rows), dim3(th), smem, s, (const bf16*)y, x, (bf16*)out_e, a);
   } else {
-    if (vec) DLI_LAUNCH("layer_close", (layer_close_kernel<float, 4>), dim3(rows), dim3(th), 0, s, (const float*)y, x, (float*)out_e, a);
-    else DLI_LAUNCH("layer_close", (layer_close_kernel<float, 1>), dim3(rows), dim3(th), 0, s, (const float*)y, x, (float*)out_e, a);
+    if (vec) DLI_LAUNCH("layer_close", (layer_close_kernel<float, 4>), dim3(rows), dim3(th), smem, s, (const float*)y, x, (float*)out_e, a);
+    else DLI_LAUNCH("layer_close", (layer_close_kernel<float, 1>), dim3(rows), dim3(th), smem, s, (const float*)y, x, (float*)out_e, a);
   }
   return DLI_OK;
 }

@@ -409,10 +409,33 @@ linear_any_kernel(const E* __restrict__ x, const E* __restrict__ w, O* __restric
 // act[m, f] = silu(gu[m, f] + b[f]) * (gu[m, F + f] + b[F + f]); bias [2F] fp32 or NULL
 template <typename E>
 __global__ void __launch_bounds__(256)
-silu_mul_kernel(const E* __restrict__ gu, E* __restrict__ act, int F, int ld, const float* __restrict__ bias) {
+silu_mul_kernel(const E* __restrict__ gu, E* __restrict__ act, int F, int ld, const float* __restrict__ bias, int vec) {
   pdl_wait();
   pdl_trigger();
   const size_t m = blockIdx.x;
+  if (vec) {
+    // 16 bytes per access: V consecutive channels of the gate half and of the up half
+    constexpr int V = 16 / (int)sizeof(E);
+    for (int f = (blockIdx.y * blockDim.x + threadIdx.x) * V; f < F; f += blockDim.x * gridDim.y * V) {
+      float g[V], u[V], o[V];
+      if constexpr (sizeof(E) == 2) {
+        unpack8(ld_16B(gu + m * ld + f), g);
+        unpack8(ld_16B(gu + m * ld + F + f), u);
+      } else {
+        const float4 a4 = *reinterpret_cast<const float4*>(gu + m * ld + f), b4 = *reinterpret_cast<const float4*>(gu + m * ld + F + f);
+        g[0] = a4.x; g[1] = a4.y; g[2] = a4.z; g[3] = a4.w;
+        u[0] = b4.x; u[1] = b4.y; u[2] = b4.z; u[3] = b4.w;
+      }
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        if (bias) { g[k] += bias[f + k]; u[k] += bias[F + f + k]; }
+        o[k] = to_f(from_f<E>(silu_f(g[k]))) * u[k];
+      }
+      if constexpr (sizeof(E) == 2) st_16B(act + m * F + f, pack8(o));
+      else *reinterpret_cast<float4*>(act + m * F + f) = make_float4(o[0], o[1], o[2], o[3]);
+    }
+    return;
+  }
   for (int f = blockIdx.y * blockDim.x + threadIdx.x; f < F; f += blockDim.x * gridDim.y) {
     float g = to_f(gu[m * ld + f]), u = to_f(gu[m * ld + F + f]);
     if (bias) { g += bias[f]; u += bias[F + f]; }
@@ -702,9 +725,12 @@ int dli_silu_mul(const void* gu, void* act, int M, int F, int ld, int dt, const 
   DT_CHECK(dt);
   if (M <= 0) return DLI_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const dim3 grid(M, M <= 64 ? (F + 1023) / 1024 : 1);  // few rows: a row's channels go to several CTAs
-  if (dt == 0) DLI_LAUNCH("silu_mul", silu_mul_kernel<bf16>, grid, dim3(256), 0, s, (const bf16*)gu, (bf16*)act, F, ld, bias);
-  else DLI_LAUNCH("silu_mul", silu_mul_kernel<float>, grid, dim3(256), 0, s, (const float*)gu, (float*)act, F, ld, bias);
+  const int per = dt == 0 ? 8 : 4;
+  const int vec = F % per == 0 && ld % per == 0 && aligned16(gu) && aligned16(act);
+  const int work = F / (vec ? per : 1);
+  const dim3 grid(M, M <= 64 ? (work + 1023) / 1024 : (work >= 2048 ? 2 : 1));  // few or long rows: a row's channels go to several CTAs
+  if (dt == 0) DLI_LAUNCH("silu_mul", silu_mul_kernel<bf16>, grid, dim3(256), 0, s, (const bf16*)gu, (bf16*)act, F, ld, bias, vec);
+  else DLI_LAUNCH("silu_mul", silu_mul_kernel<float>, grid, dim3(256), 0, s, (const float*)gu, (float*)act, F, ld, bias, vec);
   return DLI_OK;
 }
 

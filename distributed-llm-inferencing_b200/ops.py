@@ -795,12 +795,19 @@ def moe_sel(x, w_gu, w_down, sel_idx, sel_w, act_sel, y, n_exp, top, ff, limit, 
 # ---------------------------------------------------------------------------------------------------------------
 # Pre-norm layers with layer scale, token shift and depth average (prenorm_rows.cu)
 def layer_close(x, y=None, bias=None, idw=None, h_in=None, ls=None, xs=None, n_prev=0, dwa=None, w_next=None, shift=None,
-                tail=None, ent=None, out_f=None, out_e=None, eps: float = 1e-6):
+                tail=None, ent=None, out_f=None, out_e=None, eps: float = 1e-6, route=None):
     """x += ls * (y + bias + idw[:, None] * h_in) (x float32 in place; y in the element type); with dwa (float32 [n_prev + 1])
     the result is stored as xs[n_prev] and x becomes sum_j dwa[j] * xs[j] (xs float32 [n, rows_cap, d]); with w_next the
     normed x goes to out_f (float32) / out_e (element type); shift (steps of one row per entry): the normed row is mixed
-    with the slot's stored row (tail float32 [slots, d]), which it replaces."""
+    with the slot's stored row (tail float32 [slots, d]), which it replaces.  route: moe_route's arguments after h as a
+    dict (w_router, correction, wts, idw, sel_idx, sel_w, n_real, top, groups, keep, wscale, renorm) — the router then runs on
+    the rows of out_f in the same kernel."""
     _f32(x, bias, idw, h_in, ls, xs, dwa, w_next, shift, tail, out_f), _i32(ent)
+    r = route or {}
+    if route is not None:
+        _f32(r["w_router"], r.get("correction"), r["wts"], r["idw"], r["sel_w"]), _i32(r["sel_idx"])
+        if out_f is None or r["w_router"].shape[1] != x.shape[1]:
+            raise ValueError("layer_close: the router reads the float32 normed rows")
     for t in (y, out_e):
         if t is not None:
             _req(t, t.dtype)
@@ -809,7 +816,10 @@ def layer_close(x, y=None, bias=None, idw=None, h_in=None, ls=None, xs=None, n_p
         raise ValueError("layer_close: the depth average needs n_prev + 1 weights and stored results")
     _call("dli_layer_close", 1, _p(y), _p(bias), _p(idw), _p(h_in), _p(ls), _p(x), _p(xs), xs.stride(0) if xs is not None else 0,
           int(n_prev), _p(dwa), _p(w_next), _p(shift), _p(tail), _p(ent), _p(out_f), _p(out_e), x.shape[0], x.shape[1],
-          float(eps), _dt(ref) if ref is not None else 1, _stream())
+          float(eps), _dt(ref) if ref is not None else 1, _p(r.get("w_router")), _p(r.get("correction")), _p(r.get("wts")),
+          _p(r.get("idw")), _p(r.get("sel_idx")), _p(r.get("sel_w")), r["w_router"].shape[0] if route is not None else 0,
+          int(r.get("n_real", 0)), int(r.get("top", 0)), int(r.get("groups", 1)), int(r.get("keep", 1)),
+          float(r.get("wscale", 1.0)), 1 if r.get("renorm", True) else 0, _stream())
     return x
 
 

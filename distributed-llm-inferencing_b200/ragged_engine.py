@@ -907,13 +907,15 @@ class RaggedEngine:
             close = {"ls": P["ls2"], "bias": P["down_b"]}
         elif L.moe is not None:
             e = L.moe
-            ops.layer_close(x, y, ls=P["ls1"], w_next=P["norm2"], out_f=hn, out_e=he, eps=s.eps)
             y_last = self._y2[:rows]
             wts = self._wts[:rows * e.experts].view(rows, e.experts)
             idw = self._idw[:rows]
             sel_idx, sel_w = self._sel_idx[:rows * e.top].view(rows, e.top), self._sel_w[:rows * e.top].view(rows, e.top)
-            ops.moe_route(hn, P["w_router"], P["corr"], wts, idw, sel_idx, sel_w, e.experts, e.top, groups=e.groups,
-                          keep=e.keep, wscale=e.route_scale, renorm=e.renorm)
+            # the kernel that closes the mixer and norms the row also routes it
+            ops.layer_close(x, y, ls=P["ls1"], w_next=P["norm2"], out_f=hn, out_e=he, eps=s.eps,
+                            route=dict(w_router=P["w_router"], correction=P["corr"], wts=wts, idw=idw, sel_idx=sel_idx, sel_w=sel_w,
+                                       n_real=e.experts, top=e.top, groups=e.groups, keep=e.keep, wscale=e.route_scale,
+                                       renorm=e.renorm))
             if self._moe_sel_ok(e, rows):
                 # decode rows of a sparse enough mixture: stream only the chosen experts' weights
                 n_sel = e.top * e.ff + e.shared_ff

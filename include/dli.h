@@ -589,10 +589,14 @@ int dli_moe_sel_bf16(const void* x, const void* w_gu, const void* w_down, const 
  *   x = v;  w_next != NULL: h = v / sqrt(mean(v^2) + eps) * w_next -> out_f (fp32) and / or out_e (element type)
  *   shift != NULL (steps of ONE row per entry): h <- h + (t - h) * shift with t the slot's stored row (zeros at
  *                position 0), and the slot's row becomes the unshifted h.  tail [slots, d].
+ *   w_router != NULL (with out_f, without shift): dli_moe_route's router runs on the row of out_f in the same kernel
+ *                (arguments as there; r_wts / r_idw / r_sel_idx / r_sel_w are its outputs).
  * dli_token_shift_ragged: the same shift for any step, on normed rows h [rows, d] fp32 -> out (element type). */
 int dli_layer_close(const void* y, const float* bias, const float* idw, const float* h_in, const float* ls, float* x,
                     float* xs, size_t xs_stride, int n_prev, const float* dwa, const float* w_next, const float* shift,
                     float* tail, const int32_t* ent, float* out_f, void* out_e, int rows, int d, float eps, int dt,
+                    const float* w_router, const float* correction, float* r_wts, float* r_idw, int32_t* r_sel_idx,
+                    float* r_sel_w, int n_out, int n_real, int top, int groups, int keep, float wscale, int renorm,
                     dli_stream_t stream);
 int dli_token_shift_ragged(const float* h, const float* shift, float* tail, const int32_t* row_ent, const int32_t* ent,
                            void* out, int rows, int d, int dt, dli_stream_t stream);

@@ -147,18 +147,21 @@ def test_layer_close_with_the_shift_of_single_rows_and_the_ragged_shift_agree_wi
 
 
 def test_silu_mul_with_biases():
+    """Sizes that take the 2-byte and the 16-byte accesses, a row stride above 2F."""
     from dli_b200 import ops
 
     torch.manual_seed(3)
-    for dt, tol in ((torch.float32, 1e-5), (torch.bfloat16, 0.03)):
-        gu = torch.randn(6, 2 * 20 + 4).to(dt)          # a row stride above 2F
-        b = torch.randn(40)
-        out = torch.empty(6, 20, dtype=dt, device=DEV)
-        ops.silu_mul(gu.to(DEV), out, bias=b.to(DEV))
-        g, u = gu[:, :20].double() + b[:20].double(), gu[:, 20:40].double() + b[20:].double()
-        assert (out.double().cpu() - R.silu(g) * u).abs().max() < tol
-        ops.silu_mul(gu.to(DEV), out)
-        assert (out.double().cpu() - R.silu(gu[:, :20].double()) * gu[:, 20:40].double()).abs().max() < tol
+    for F, ld in ((20, 44), (24, 56), (512, 1024)):
+        for dt, tol in ((torch.float32, 1e-5), (torch.bfloat16, 0.03)):
+            gu = torch.randn(6, ld).to(dt)
+            b = torch.randn(2 * F)
+            out = torch.empty(6, F, dtype=dt, device=DEV)
+            ops.silu_mul(gu.to(DEV), out, bias=b.to(DEV))
+            g, u = gu[:, :F].double() + b[:F].double(), gu[:, F:2 * F].double() + b[F:].double()
+            assert (out.double().cpu() - R.silu(g) * u).abs().max() < tol * max(1.0, float((R.silu(g) * u).abs().max()))
+            ops.silu_mul(gu.to(DEV), out)
+            ref = R.silu(gu[:, :F].double()) * gu[:, F:2 * F].double()
+            assert (out.double().cpu() - ref).abs().max() < tol * max(1.0, float(ref.abs().max()))
 
 
 # ---------------------------------------------------------------------------------------------------- attention
@@ -377,6 +380,36 @@ def test_router_with_groups_against_oracle(shape):
     plain, _ = R.route(h.double(), w.double(), torch.zeros(E + I, dtype=F64), dict(r, groups={"count": 1, "keep": 1}))
     if count > 1 and keep < count:
         assert any(sorted(plain[t].tolist()) != sorted(idx[t].tolist()) for t in range(rows))
+
+
+@pytest.mark.parametrize("rows,d", [(3, 24), (70, 40), (5, 2048)])
+def test_router_inside_the_closing_kernel_equals_the_router_alone(rows, d):
+    """The closing kernel norms a row and routes it at once; choice and weights are those of the router kernel on the
+    normed rows it wrote, bit for bit."""
+    from dli_b200 import ops
+
+    torch.manual_seed(10)
+    E, I, top, count, keep, scale = 6, 2, 3, 4, 2, 1.7
+    x, y = torch.randn(rows, d, device=DEV), torch.randn(rows, d, device=DEV).to(torch.bfloat16)
+    ls, wn = torch.rand(d, device=DEV) + 0.2, torch.rand(d, device=DEV) + 0.5
+    w, c = (torch.randn(E + I, d) * 0.6).to(DEV), (-1.0 - torch.rand(E + I)).to(DEV)
+    outs = []
+    for fused in (True, False):
+        wts, idw = torch.full((rows, E), 9.0, device=DEV), torch.full((rows,), 9.0, device=DEV)
+        si, sw = torch.zeros(rows, top, dtype=torch.int32, device=DEV), torch.zeros(rows, top, device=DEV)
+        hn, he = torch.empty(rows, d, device=DEV), torch.empty(rows, d, dtype=torch.bfloat16, device=DEV)
+        xc = x.clone()
+        r = dict(w_router=w, correction=c, wts=wts, idw=idw, sel_idx=si, sel_w=sw, n_real=E, top=top, groups=count, keep=keep,
+                 wscale=scale, renorm=False)
+        ops.layer_close(xc, y, ls=ls, w_next=wn, out_f=hn, out_e=he, eps=1e-5, route=r if fused else None)
+        if not fused:
+            ops.moe_route(hn, w, c, wts, idw, si, sw, E, top, groups=count, keep=keep, wscale=scale, renorm=False)
+        outs.append([t.cpu() for t in (xc, hn, he.float(), wts, idw, si, sw)])
+    for a_, b_ in zip(*outs):
+        assert torch.equal(a_, b_)
+    idx, wt = R.route(outs[0][1].double(), w.double().cpu(), c.double().cpu(),
+                      {"experts": E, "identity": I, "top": top, "scale": scale, "groups": {"count": count, "keep": keep}})
+    assert all(sorted(outs[0][5][t].tolist()) == sorted(idx[t].tolist()) for t in range(rows))
 
 
 def moe_tensors(E, I, ff, d, seed):
