@@ -240,7 +240,7 @@ int dli_layer_close(const void* y, const float* bias, const float* idw, const fl
                    al(out_e, dt == 0 ? 8 : 16);
   const int per = vec ? 4 : 1;
   int th = (rows <= 64 && d >= 2048 * per) ? 1024 : (d >= 256 * per ? 256 : 128);
-  if (w_router && th < 256) th = 256;  // a warp per router output
+  if (w_router && th < (rows <= 64 ? 512 : 256)) th = rows <= 64 ? 512 : 256;  // a warp per router output; few rows: more warps for the logits
   if (dt == 0) {
     if (vec) DLI_LAUNCH("layer_close", (layer_close_kernel<bf16, 4>), dim3(rows), dim3(th), smem, s, (const bf16*)y, x, (bf16*)out_e, a);
     else DLI_LAUNCH("layer_close", (layer_close_kernel<bf16, 1>), dim3(rows), dim3(th), smem, s, (const bf16*)y, x, (bf16*)out_e, a);

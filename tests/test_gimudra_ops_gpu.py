@@ -385,7 +385,7 @@ def test_router_with_groups_against_oracle(shape):
 @pytest.mark.parametrize("rows,d", [(3, 24), (70, 40), (5, 2048)])
 def test_router_inside_the_closing_kernel_equals_the_router_alone(rows, d):
     """The closing kernel norms a row and routes it at once; choice and weights are those of the router kernel on the
-    normed rows it wrote, bit for bit."""
+    normed rows it wrote, bit for bit, and the rows themselves are those of the kernel without the router."""
     from dli_b200 import ops
 
     torch.manual_seed(10)
@@ -393,23 +393,27 @@ def test_router_inside_the_closing_kernel_equals_the_router_alone(rows, d):
     x, y = torch.randn(rows, d, device=DEV), torch.randn(rows, d, device=DEV).to(torch.bfloat16)
     ls, wn = torch.rand(d, device=DEV) + 0.2, torch.rand(d, device=DEV) + 0.5
     w, c = (torch.randn(E + I, d) * 0.6).to(DEV), (-1.0 - torch.rand(E + I)).to(DEV)
-    outs = []
-    for fused in (True, False):
-        wts, idw = torch.full((rows, E), 9.0, device=DEV), torch.full((rows,), 9.0, device=DEV)
-        si, sw = torch.zeros(rows, top, dtype=torch.int32, device=DEV), torch.zeros(rows, top, device=DEV)
-        hn, he = torch.empty(rows, d, device=DEV), torch.empty(rows, d, dtype=torch.bfloat16, device=DEV)
-        xc = x.clone()
-        r = dict(w_router=w, correction=c, wts=wts, idw=idw, sel_idx=si, sel_w=sw, n_real=E, top=top, groups=count, keep=keep,
-                 wscale=scale, renorm=False)
-        ops.layer_close(xc, y, ls=ls, w_next=wn, out_f=hn, out_e=he, eps=1e-5, route=r if fused else None)
-        if not fused:
-            ops.moe_route(hn, w, c, wts, idw, si, sw, E, top, groups=count, keep=keep, wscale=scale, renorm=False)
-        outs.append([t.cpu() for t in (xc, hn, he.float(), wts, idw, si, sw)])
-    for a_, b_ in zip(*outs):
+
+    def buffers():
+        return (torch.full((rows, E), 9.0, device=DEV), torch.full((rows,), 9.0, device=DEV),
+                torch.zeros(rows, top, dtype=torch.int32, device=DEV), torch.zeros(rows, top, device=DEV))
+
+    kw = dict(n_real=E, top=top, groups=count, keep=keep, wscale=scale, renorm=False)
+    wts, idw, si, sw = buffers()
+    hn, he = torch.empty(rows, d, device=DEV), torch.empty(rows, d, dtype=torch.bfloat16, device=DEV)
+    xc = x.clone()
+    ops.layer_close(xc, y, ls=ls, w_next=wn, out_f=hn, out_e=he, eps=1e-5,
+                    route=dict(w_router=w, correction=c, wts=wts, idw=idw, sel_idx=si, sel_w=sw, **kw))
+    wts2, idw2, si2, sw2 = buffers()
+    ops.moe_route(hn, w, c, wts2, idw2, si2, sw2, E, top, groups=count, keep=keep, wscale=scale, renorm=False)
+    for a_, b_ in ((wts, wts2), (idw, idw2), (si, si2), (sw, sw2)):
         assert torch.equal(a_, b_)
-    idx, wt = R.route(outs[0][1].double(), w.double().cpu(), c.double().cpu(),
+    hn2, he2, xc2 = torch.empty_like(hn), torch.empty_like(he), x.clone()
+    ops.layer_close(xc2, y, ls=ls, w_next=wn, out_f=hn2, out_e=he2, eps=1e-5)
+    assert torch.equal(xc, xc2) and (hn - hn2).abs().max() < 1e-5 and (he.float() - he2.float()).abs().max() < 0.05
+    idx, wt = R.route(hn.double().cpu(), w.double().cpu(), c.double().cpu(),
                       {"experts": E, "identity": I, "top": top, "scale": scale, "groups": {"count": count, "keep": keep}})
-    assert all(sorted(outs[0][5][t].tolist()) == sorted(idx[t].tolist()) for t in range(rows))
+    assert all(sorted(si[t].tolist()) == sorted(idx[t].tolist()) for t in range(rows))
 
 
 def moe_tensors(E, I, ff, d, seed):
