@@ -212,6 +212,36 @@ def test_bfloat16_sizes_of_the_tensor_core_kernels():
     assert rel_err(both[:1], ref[150:151]).max() < 0.3 and close16(rel_err(both[1:], ref[:90]))
 
 
+@pytest.mark.parametrize("dims", [(128, 64, 128, 256), (64, 128, 64, 64)])
+def test_bfloat16_tensor_core_tiles_with_unequal_key_and_value_sizes(dims):
+    """The tensor-core tiles whose key and value sizes differ, with a reader of layer 0's cache, in whole prompts, portions
+    and token-by-token tails.  The routers' corrections are multiples of 3, so the choice never hangs on bf16 rounding
+    (the weights still are the scores) and every position is held to the bound."""
+    from dli_b200 import gimudra, ops
+    from dli_b200.ragged_engine import RaggedEngine
+
+    d0, v0, d2, v2 = dims
+    cfg = config([(attention(heads=2, kv_heads=1, dim=d0, vdim=v0, scale=0.09, size=70), dense(ff=96)),
+                  (attention(heads=2, kv_heads=1, dim=d0, vdim=v0, scale=0.09, size=33, kv_from=0), moe(experts=4, identity=0, top=2, count=2, keep=2, ff=32)),
+                  (attention(heads=1, kv_heads=1, dim=d2, vdim=v2, scale=0.09, size=100), moe(experts=5, identity=1, top=2, count=3, keep=2, ff=16))],
+                 width=64, vocab=200)
+    spec = gimudra.spec_from_config(cfg)
+    sd = gimudra.random_state_dict(spec, seed=1, std=0.15)
+    for k in list(sd):
+        if k.endswith("correction"):
+            n = sd[k].numel()
+            sd[k] = (torch.randperm(n, generator=torch.Generator().manual_seed(n)).float() * 3.0).to(sd[k].dtype)
+    eng = RaggedEngine(spec, max_batch=4, max_seq_len=512, page_size=4, dtype=torch.bfloat16)
+    eng.load_tensors(gimudra.model_tensors(spec, sd))
+    assert all(ops.attn_ragged_tc_supported(L.mixer.dim, L.mixer.vdim, torch.bfloat16) for L in eng.spec.layers)
+    toks = prompt(300, cfg["vocab"], 5)
+    ref = R.forward(cfg, sd, toks)
+    runs = [run_schedule(eng, toks, cuts) for cuts in ([300], [100, 3, 64, 63, 70], [17, 2, 130, 2, 100])]
+    for got in runs:
+        assert rel_err(got, ref).max() < TOL16
+    assert rel_err(runs[1], runs[0].double()).max() < TOL16
+
+
 def test_mixed_batches_of_unequal_requests_match_each_alone():
     """Four requests of different lengths move through shared steps in portions of different sizes, some decoding
     while others are in their prompt, some skipping steps; each position equals the oracle's for that request alone."""
